@@ -20,8 +20,8 @@ immediate.
 
 Beside the pages, every request holds one state slot.  A mixer with per-request
 state of fixed size (``StateNeed``) gets a tensor [max_requests, *shape] per layer,
-and the slot's rows are zeroed when a request opens.  This architecture has no
-such mixer; the slots are handed out and taken back all the same.
+and the slot's rows are zeroed when a request opens.  Models without such a mixer
+hold and return their slots all the same.
 """
 from __future__ import annotations
 
@@ -88,7 +88,10 @@ class CacheGroup:
     slots: List[int]           # cache slots (layer calls) that live in this group
     page_size: int
     pool: IdPool
-    storage: Optional[torch.Tensor] = None   # [len(slots), 2, pages, kv heads, page_size, head_dim]
+    storage: Optional[torch.Tensor] = None   # [len(slots), 2, pages, kv heads, page_size, head_dim]; flat when the
+                                             # values have another size than the keys
+    k_store: Optional[torch.Tensor] = None   # [len(slots), pages, kv heads, page_size, head_dim]
+    v_store: Optional[torch.Tensor] = None   # [len(slots), pages, kv heads, page_size, value size]
 
     @property
     def window(self) -> Optional[int]:
@@ -134,7 +137,7 @@ class CacheManager:
                 if isinstance(item, PagedKVNeed):
                     if item.window is not None and item.window <= 0:
                         raise ValueError(f"cache slot {slot}: window {item.window} must be positive")
-                    key = (item.n_kv_heads, item.head_dim, item.window)
+                    key = (item.n_kv_heads, item.head_dim, item.window, item.value_dim)
                     g = by_key.get(key)
                     if g is None:
                         g = CacheGroup(len(self.groups), item, [], page_size, IdPool(num_pages, "page"))
@@ -155,8 +158,15 @@ class CacheManager:
                     raise TypeError(f"cache slot {slot}: unknown need {item!r}")
         if allocate:
             for g in self.groups:
-                g.storage = torch.zeros((len(g.slots), 2, num_pages, g.need.n_kv_heads, page_size,
-                                         g.need.head_dim), dtype=dtype, device=self.device)
+                L, G, hd, vd = len(g.slots), g.need.n_kv_heads, g.need.head_dim, g.need.value_dim
+                if vd == hd:
+                    g.storage = torch.zeros((L, 2, num_pages, G, page_size, hd), dtype=dtype, device=self.device)
+                    g.k_store, g.v_store = g.storage[:, 0], g.storage[:, 1]
+                else:
+                    rows = L * num_pages * G * page_size
+                    g.storage = torch.zeros(rows * (hd + vd), dtype=dtype, device=self.device)
+                    g.k_store = g.storage[:rows * hd].view(L, num_pages, G, page_size, hd)
+                    g.v_store = g.storage[rows * hd:].view(L, num_pages, G, page_size, vd)
         self.state_slots = IdPool(max_requests, "state slot")
         self.live: Dict[int, RequestCache] = {}
         self._next_rid = 0
@@ -166,7 +176,7 @@ class CacheManager:
         """Device bytes that one more page in EVERY group's pool costs: keys and values of
         all layers of all groups (the pools have the same number of pages)."""
         esize = torch.empty((), dtype=self.dtype).element_size()
-        return sum(len(g.slots) * 2 * g.need.n_kv_heads * self.page_size * g.need.head_dim * esize
+        return sum(len(g.slots) * g.need.n_kv_heads * self.page_size * (g.need.head_dim + g.need.value_dim) * esize
                    for g in self.groups)
 
     @classmethod
@@ -188,7 +198,7 @@ class CacheManager:
         """Cache bytes that one more token of context costs in the groups that keep
         every key."""
         esize = torch.empty((), dtype=self.dtype).element_size()
-        return sum(len(g.slots) * 2 * g.need.n_kv_heads * g.need.head_dim * esize
+        return sum(len(g.slots) * g.need.n_kv_heads * (g.need.head_dim + g.need.value_dim) * esize
                    for g in self.groups if g.window is None)
 
     def pages_ever_needed(self, total_tokens: int) -> List[int]:
@@ -322,7 +332,7 @@ class CacheManager:
             if slot in self.slot_group:
                 g = self.groups[self.slot_group[slot]]
                 layer = self.slot_layer[slot]
-                k, v = g.storage[layer, 0], g.storage[layer, 1]
+                k, v = g.k_store[layer], g.v_store[layer]
                 table = block_tables[g.index]
             out.append(LayerCache(k=k, v=v, block_table=table, state=self.state.get(slot),
                                   writes=True, page_size=self.page_size))

@@ -1,6 +1,7 @@
 from .base import (ConfigError, ModelConfig, build_model_spec, known_architectures, load_config,
                    lookup_architecture, parse_config, register_architecture)
 from .llama import LlamaConfig
+from .sozarax import SozaraxConfig
 
-__all__ = ["ConfigError", "ModelConfig", "LlamaConfig", "build_model_spec", "known_architectures",
+__all__ = ["ConfigError", "ModelConfig", "LlamaConfig", "SozaraxConfig", "build_model_spec", "known_architectures",
            "load_config", "lookup_architecture", "parse_config", "register_architecture"]

@@ -58,8 +58,10 @@ def lookup_architecture(name: str):
 
 def parse_config(d: dict) -> ModelConfig:
     archs = d.get("architectures")
+    if archs is None and isinstance(d.get("architecture"), str):
+        archs = [d["architecture"]]          # some formats name one class in a plain string
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ConfigError("config.json has no 'architectures' list naming the model class")
+        raise ConfigError("config.json has no 'architectures' list (or 'architecture' string) naming the model class")
     config_cls, _ = lookup_architecture(archs[0])
     return config_cls.from_dict(d)
 

@@ -50,7 +50,49 @@ __global__ void silu_mul_vec4_kernel(bf16* __restrict__ out, int64_t out_stride,
     }
 }
 
+// out = f(in) elementwise on float32 input rows: op 0 the square of relu, op 1 tanh.
+template <typename T>
+__global__ void unary_kernel(T* __restrict__ out, int64_t out_stride, const float* __restrict__ in, int64_t in_stride,
+                             int n, int f, int op) {
+    griddep_wait();
+    griddep_launch();
+    const int64_t total = (int64_t)n * f;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = idx / f;
+        const int c = (int)(idx - r * f);
+        const float z = in[r * in_stride + c];
+        float v;
+        if (op == 0) {
+            const float p = fmaxf(z, 0.f);
+            v = p * p;
+        } else {
+            v = tanhf(z);
+        }
+        out[r * out_stride + c] = from_f32<T>(v);
+    }
+}
+
 }  // namespace
+
+// out [n][f] in the element type `dtype`, in float32 [n][f], dense rows at their strides.
+extern "C" int kllm_unary(void* out, int64_t out_stride, const void* in, int64_t in_stride, int n, int f, int op,
+                          int dtype, void* stream) {
+    if (n <= 0 || f <= 0) return 0;
+    if (op < 0 || op > 1) KLLM_FAIL("unary: unknown function %d", op);
+    cudaStream_t s = (cudaStream_t)stream;
+    int64_t blocks = ((int64_t)n * f + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (dtype == KLLM_F32)
+        kllm_launch((unary_kernel<float>), dim3((unsigned)blocks), dim3(256), 0, s, (float*)out, out_stride,
+                    (const float*)in, in_stride, n, f, op);
+    else if (dtype == KLLM_BF16)
+        kllm_launch((unary_kernel<bf16>), dim3((unsigned)blocks), dim3(256), 0, s, (bf16*)out, out_stride,
+                    (const float*)in, in_stride, n, f, op);
+    else
+        KLLM_FAIL("unary: unknown element type %d", dtype);
+    KLLM_LAUNCH_STATUS();
+}
 
 // dtype: element type of out; in_dtype: element type of gate and up.
 extern "C" int kllm_silu_mul(void* out, int64_t out_stride, const void* gate, int64_t gate_stride,

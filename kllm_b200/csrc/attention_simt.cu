@@ -57,21 +57,21 @@ __device__ __forceinline__ float half_warp_sum(float v) {
     return v;
 }
 
-// NC: float4 groups of output dims per thread and row, ceil(hd / 64) rounded up to 1, 2 or 4.
+// NC: float4 groups of output dims per thread and row, ceil(vd / 64) rounded up to 1, 2 or 4.
 template <typename T, int NC>
 __global__ void __launch_bounds__(THREADS)
 attn_simt_kernel(T* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
                  const T* __restrict__ q, int64_t q_stride, const T* __restrict__ kcache,
                  const T* __restrict__ vcache, const int* __restrict__ q_start, const int* __restrict__ start_pos,
                  const int* __restrict__ block_table, int max_blocks, int n_requests, int n_heads, int n_kv, int hd,
-                 int page_size, int window, float scale, int qt, int chunk, int max_splits,
+                 int vd, int page_size, int window, float scale, int qt, int chunk, int max_splits,
                  const float* __restrict__ slopes) {
     extern __shared__ __align__(16) float sm[];
-    const int ld = hd + 4;
+    const int ld = hd + 4, ldv = vd + 4;
     float* Qs = sm;
     float* Ks = Qs + ROWS * ld;
     float* Vs = Ks + KEYS * ld;
-    float* Ps = Vs + KEYS * ld;
+    float* Ps = Vs + KEYS * ldv;
     griddep_wait();
     griddep_launch();
 
@@ -112,7 +112,7 @@ attn_simt_kernel(T* __restrict__ out, float* __restrict__ part_o, float* __restr
     }
     const int* table = block_table + (int64_t)s * max_blocks;
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
-    const int hd4 = hd >> 2;
+    const int hd4 = hd >> 2, vd4 = vd >> 2;
 
     for (int e = tid; e < ROWS * hd4; e += THREADS) {
         const int r = e / hd4, c = e - r * hd4;
@@ -150,17 +150,19 @@ attn_simt_kernel(T* __restrict__ out, float* __restrict__ part_o, float* __restr
             int64_t off = 0;
             if (ok) {
                 const int lp = kp / page_size;
-                off = (((int64_t)table[lp] * n_kv + g) * page_size + (kp - lp * page_size)) * hd;
+                off = ((int64_t)table[lp] * n_kv + g) * page_size + (kp - lp * page_size);
             }
 #pragma unroll 4
             for (int c = tid & 3; c < hd4; c += 4) {
-                float4 kv = make_float4(0.f, 0.f, 0.f, 0.f), vv = kv;
-                if (ok) {
-                    kv = load4(kcache + off + 4 * c);
-                    vv = load4(vcache + off + 4 * c);
-                }
+                float4 kv = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (ok) kv = load4(kcache + off * hd + 4 * c);
                 *reinterpret_cast<float4*>(Ks + k * ld + 4 * c) = kv;
-                *reinterpret_cast<float4*>(Vs + k * ld + 4 * c) = vv;
+            }
+#pragma unroll 4
+            for (int c = tid & 3; c < vd4; c += 4) {
+                float4 vv = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (ok) vv = load4(vcache + off * vd + 4 * c);
+                *reinterpret_cast<float4*>(Vs + k * ldv + 4 * c) = vv;
             }
         }
         __syncthreads();
@@ -236,8 +238,8 @@ attn_simt_kernel(T* __restrict__ out, float* __restrict__ part_o, float* __restr
 #pragma unroll
                     for (int c = 0; c < NC; c++) {
                         const int d = 4 * tx + 64 * c;
-                        if (d < hd) {
-                            const float4 v = *reinterpret_cast<const float4*>(Vs + (k + kk) * ld + d);
+                        if (d < vd) {
+                            const float4 v = *reinterpret_cast<const float4*>(Vs + (k + kk) * ldv + d);
 #pragma unroll
                             for (int i = 0; i < 4; i++) {
                                 if (i >= ri) break;
@@ -263,16 +265,16 @@ attn_simt_kernel(T* __restrict__ out, float* __restrict__ part_o, float* __restr
 #pragma unroll
             for (int c = 0; c < NC; c++) {
                 const int d = 4 * tx + 64 * c;
-                if (d < hd)
-                    store4(out + row * hd + d, make_float4(acc[i][c].x * inv, acc[i][c].y * inv,
+                if (d < vd)
+                    store4(out + row * vd + d, make_float4(acc[i][c].x * inv, acc[i][c].y * inv,
                                                            acc[i][c].z * inv, acc[i][c].w * inv));
             }
         } else {
-            float* po = part_o + (row * max_splits + split) * hd;
+            float* po = part_o + (row * max_splits + split) * vd;
 #pragma unroll
             for (int c = 0; c < NC; c++) {
                 const int d = 4 * tx + 64 * c;
-                if (d < hd) *reinterpret_cast<float4*>(po + d) = acc[i][c];
+                if (d < vd) *reinterpret_cast<float4*>(po + d) = acc[i][c];
             }
             if (tx == 0) *reinterpret_cast<float2*>(part_ml + (row * max_splits + split) * 2) = make_float2(m[i], l[i]);
         }
@@ -552,18 +554,18 @@ attn_simt_merge_kernel(T* __restrict__ out, const float* __restrict__ part_o, co
     }
 }
 
-size_t smem_bytes(int hd) { return (size_t)(3 * 64 * (hd + 4) + ROWS * PLD) * sizeof(float); }
+size_t smem_bytes(int hd, int vd) { return (size_t)(2 * 64 * (hd + 4) + 64 * (vd + 4) + ROWS * PLD) * sizeof(float); }
 
 template <typename T, int NC>
 int launch(void* out, float* part_o, float* part_ml, const void* q, int64_t q_stride, const void* kcache,
            const void* vcache, const int* q_start, const int* start_pos, const int* block_table, int max_blocks,
-           int n_requests, int max_tiles, int n_heads, int n_kv, int hd, int page_size, int window, float scale,
+           int n_requests, int max_tiles, int n_heads, int n_kv, int hd, int vd, int page_size, int window, float scale,
            int qt, int chunk, int max_splits, const float* slopes, cudaStream_t s) {
     auto kern = attn_simt_kernel<T, NC>;
     static bool raised = false;
-    const size_t smem = smem_bytes(hd);
+    const size_t smem = smem_bytes(hd, vd);
     if (!raised) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes(64 * NC));
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes(256, 64 * NC));
         if (e != cudaSuccess) {
             snprintf(g_kllm_err, sizeof(g_kllm_err), "attention (simt): shared memory limit: %s", cudaGetErrorString(e));
             return (int)e;
@@ -572,29 +574,31 @@ int launch(void* out, float* part_o, float* part_ml, const void* q, int64_t q_st
     }
     kllm_launch(kern, dim3(max_tiles * n_kv, 1, chunk > 0 ? max_splits : 1), dim3(THREADS), smem, s, (T*)out, part_o,
                 part_ml, (const T*)q, q_stride, (const T*)kcache, (const T*)vcache, q_start, start_pos, block_table,
-                max_blocks, n_requests, n_heads, n_kv, hd, page_size, window, scale, qt, chunk, max_splits, slopes);
+                max_blocks, n_requests, n_heads, n_kv, hd, vd, page_size, window, scale, qt, chunk, max_splits, slopes);
     KLLM_LAUNCH_STATUS();
 }
 
 }  // namespace
 
-// out [tokens, n_heads * hd] contiguous; q rows at stride q_stride (elements); caches
-// [pages, n_kv, page_size, hd]; request s brings rows q_start[s] .. q_start[s + 1]
+// out [tokens, n_heads * vd] contiguous; q rows at stride q_stride (elements); caches
+// [pages, n_kv, page_size, hd] (keys) and [pages, n_kv, page_size, vd] (values; vd is the
+// size of a head's values and of its output, equal to hd in most models); request s brings rows q_start[s] .. q_start[s + 1]
 // starting at cache position start_pos[s]; block_table [n_requests, max_blocks].
 // max_tiles: an upper bound of the sum over requests of ceil(rows of s / qt).
 // chunk == 0: every tile walks all of its keys and writes `out`.  chunk > 0 (only with
 // qt == 1): the keys of a token are cut into chunks of that many keys, at most
-// max_splits of them, whose partial results go to part_o [rows, max_splits, hd] and
+// max_splits of them, whose partial results go to part_o [rows, max_splits, vd] and
 // part_ml [rows, max_splits, 2] (row = token * n_heads + head) for kllm_attention_simt_merge.
 // slopes: optional float32 [n_heads]; slope[h] * (key position - query position) is added to
 // the scaled scores of head h.
 extern "C" int kllm_attention_simt(void* out, void* part_o, void* part_ml, const void* q, int64_t q_stride,
                                    const void* kcache, const void* vcache, const int* q_start, const int* start_pos,
                                    const int* block_table, int max_blocks, int n_requests, int max_tiles,
-                                   int n_heads, int n_kv, int hd, int page_size, int window, float scale, int qt,
+                                   int n_heads, int n_kv, int hd, int vd, int page_size, int window, float scale, int qt,
                                    int chunk, int max_splits, const float* slopes, int dtype, void* stream) {
     if (n_requests <= 0 || max_tiles <= 0) return 0;
     if (hd <= 0 || hd > 256 || hd % 4) KLLM_FAIL("attention (simt): head size %d is not a multiple of 4 up to 256", hd);
+    if (vd <= 0 || vd > 256 || vd % 4) KLLM_FAIL("attention (simt): value size %d is not a multiple of 4 up to 256", vd);
     if (n_kv <= 0 || n_heads % n_kv) KLLM_FAIL("attention (simt): %d heads over %d kv heads", n_heads, n_kv);
     const int gs = n_heads / n_kv;
     if (qt < 1 || qt * gs > ROWS) KLLM_FAIL("attention (simt): %d tokens x %d heads exceed the %d rows of a tile", qt, gs, ROWS);
@@ -606,7 +610,7 @@ extern "C" int kllm_attention_simt(void* out, void* part_o, void* part_ml, const
         KLLM_FAIL("attention (simt): operands must be aligned to four elements");
     cudaStream_t s = (cudaStream_t)stream;
     // decoding tokens in float32 at the common head sizes and group widths: the kernel in which every thread works
-    if (chunk > 0 && dtype == KLLM_F32 && (hd == 64 || hd == 128) && n_requests == max_tiles) {
+    if (chunk > 0 && dtype == KLLM_F32 && (hd == 64 || hd == 128) && vd == hd && n_requests == max_tiles) {
 #define KLLM_SIMT_DEC(HD_, GS_)                                                                                        \
     if (hd == HD_ && gs == GS_)                                                                                       \
         return launch_decode<HD_, GS_>((float*)part_o, (float*)part_ml, q, q_stride, kcache, vcache, q_start, start_pos, \
@@ -618,15 +622,15 @@ extern "C" int kllm_attention_simt(void* out, void* part_o, void* part_ml, const
     }
 #define KLLM_SIMT(T, NC)                                                                                              \
     return launch<T, NC>(out, (float*)part_o, (float*)part_ml, q, q_stride, kcache, vcache, q_start, start_pos,      \
-                         block_table, max_blocks, n_requests, max_tiles, n_heads, n_kv, hd, page_size, window, scale, \
-                         qt, chunk, max_splits, slopes, s)
+                         block_table, max_blocks, n_requests, max_tiles, n_heads, n_kv, hd, vd, page_size, window,    \
+                         scale, qt, chunk, max_splits, slopes, s)
     if (dtype == KLLM_F32) {
-        if (hd <= 64) KLLM_SIMT(float, 1);
-        if (hd <= 128) KLLM_SIMT(float, 2);
+        if (vd <= 64) KLLM_SIMT(float, 1);
+        if (vd <= 128) KLLM_SIMT(float, 2);
         KLLM_SIMT(float, 4);
     } else if (dtype == KLLM_BF16) {
-        if (hd <= 64) KLLM_SIMT(bf16, 1);
-        if (hd <= 128) KLLM_SIMT(bf16, 2);
+        if (vd <= 64) KLLM_SIMT(bf16, 1);
+        if (vd <= 128) KLLM_SIMT(bf16, 2);
         KLLM_SIMT(bf16, 4);
     }
 #undef KLLM_SIMT

@@ -1,6 +1,6 @@
 // Token embedding lookup and row gathering.
 //
-//   x[t,:] = float32(E[ids[t],:])      (reference backend/model.cu:89-95)
+//   x[t,:] = float32(E[ids[t],:]) * scale      (reference backend/model.cu:89-95; scale 1 there)
 //
 // The residual stream that this fills is float32 whatever the table's element
 // type is.  A negative id -(s + 1) stands for "the token that the sampling kernel chose
@@ -16,7 +16,8 @@ namespace {
 
 template <typename T>
 __global__ void embed_kernel(float* __restrict__ x, const T* __restrict__ table,
-                             const int* __restrict__ ids, const int* __restrict__ last_token, int d, int vocab) {
+                             const int* __restrict__ ids, const int* __restrict__ last_token, int d, int vocab,
+                             float scale) {
     griddep_wait();
     griddep_launch();
     const int t = blockIdx.x;
@@ -28,7 +29,7 @@ __global__ void embed_kernel(float* __restrict__ x, const T* __restrict__ table,
         return;
     }
     const T* er = table + (int64_t)id * d;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) xr[i] = to_f32(er[i]);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) xr[i] = to_f32(er[i]) * scale;
 }
 
 // out[r,:] = in[rows[r],:] for rows of `width` elements of `elem` bytes each
@@ -53,14 +54,14 @@ __global__ void gather_rows_kernel(char* __restrict__ out, const char* __restric
 
 // last_token: optional int32 table indexed by request slot (see above).
 extern "C" int kllm_embed(void* x, const void* table, const int* ids, const int* last_token, int n, int d,
-                          int vocab, int dtype, void* stream) {
+                          int vocab, float scale, int dtype, void* stream) {
     if (n <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = d >= 1024 ? 256 : 128;
     if (dtype == KLLM_F32)
-        kllm_launch((embed_kernel<float>), dim3(n), dim3(threads), 0, s, (float*)x, (const float*)table, ids, last_token, d, vocab);
+        kllm_launch((embed_kernel<float>), dim3(n), dim3(threads), 0, s, (float*)x, (const float*)table, ids, last_token, d, vocab, scale);
     else if (dtype == KLLM_BF16)
-        kllm_launch((embed_kernel<bf16>), dim3(n), dim3(threads), 0, s, (float*)x, (const bf16*)table, ids, last_token, d, vocab);
+        kllm_launch((embed_kernel<bf16>), dim3(n), dim3(threads), 0, s, (float*)x, (const bf16*)table, ids, last_token, d, vocab, scale);
     else
         KLLM_FAIL("embed: unknown element type %d", dtype);
     KLLM_LAUNCH_STATUS();

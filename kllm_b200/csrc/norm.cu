@@ -162,7 +162,59 @@ add_rmsnorm_warp_kernel(float* __restrict__ x, const float* __restrict__ res, bf
     }
 }
 
+// x[r,:] += y[r,:] * rsqrt(mean(y^2) + eps) * gain (a norm on a sublayer's OUTPUT before it
+// joins the residual stream), and, with `out`, out[r,:] = x[r,:] * rsqrt(mean(x^2) + eps2) *
+// gain2 of the updated row: the norm in front of the next sublayer, in the same pass.
+// One block per row; the block size follows from the width, so the order of a row's
+// additions does too.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+rmsnorm_add_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ gain, float eps,
+                   T* __restrict__ out, const float* __restrict__ gain2, float eps2, int d) {
+    __shared__ float red[32];
+    griddep_wait();
+    griddep_launch();
+    const int r = blockIdx.x;
+    float* xr = x + (int64_t)r * d;
+    const float* yr = y + (int64_t)r * d;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) ss += yr[i] * yr[i];
+    ss = block_sum(ss, red);
+    const float scale = rsqrtf(ss / (float)d + eps);
+    float s2 = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = xr[i] + yr[i] * scale * gain[i];
+        xr[i] = v;
+        s2 += v * v;
+    }
+    if (out == nullptr) return;
+    s2 = block_sum(s2, red);
+    const float scale2 = rsqrtf(s2 / (float)d + eps2);
+    T* orow = out + (int64_t)r * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) orow[i] = from_f32<T>(xr[i] * scale2 * gain2[i]);
+}
+
 }  // namespace
+
+// x float32 [n][d] (updated), y float32 [n][d], gain float32 [d]; out (optional, element type
+// `dtype`) [n][d] with gain2 [d].
+extern "C" int kllm_rmsnorm_add(void* x, const void* y, const void* gain, float eps, void* out, const void* gain2,
+                                float eps2, int n_rows, int d, int dtype, void* stream) {
+    if (n_rows <= 0) return 0;
+    if (d <= 0) KLLM_FAIL("rmsnorm_add: width %d must be positive", d);
+    if (out && !gain2) KLLM_FAIL("rmsnorm_add: a second norm needs its gain");
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = d <= 512 ? 64 : (d <= 2048 ? 128 : kThreads);
+    if (dtype == KLLM_F32)
+        kllm_launch((rmsnorm_add_kernel<float>), dim3(n_rows), dim3(threads), 0, s, (float*)x, (const float*)y,
+                    (const float*)gain, eps, (float*)out, (const float*)gain2, eps2, d);
+    else if (dtype == KLLM_BF16)
+        kllm_launch((rmsnorm_add_kernel<bf16>), dim3(n_rows), dim3(threads), 0, s, (float*)x, (const float*)y,
+                    (const float*)gain, eps, (bf16*)out, (const float*)gain2, eps2, d);
+    else
+        KLLM_FAIL("rmsnorm_add: unknown element type %d", dtype);
+    KLLM_LAUNCH_STATUS();
+}
 
 // dtype: element type of out; res_dtype: element type of res (ignored when res is NULL).
 extern "C" int kllm_add_rmsnorm(void* x, const void* res, void* out, const void* gain,

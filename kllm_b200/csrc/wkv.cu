@@ -1,0 +1,213 @@
+// A linear-attention recurrence with a per-channel decay and a bonus for the current
+// token (the time mixing of RWKV-style models), for mixed batches of prompt portions
+// and single tokens, with the state of every request in a slot of a state tensor.
+//
+// Per head, with N key channels i and N value channels j and a state S [N][N] that starts
+// at zero for a new request:
+//
+//     a_ij   = k_i v_j
+//     o_j    = sum_i r_i (S_ij + u_i a_ij)          the bonus u acts on the current token only
+//     S_ij  <- w_i S_ij + a_ij                       w_i = exp(-exp(z_i + w0_i)) in (0, 1)
+//
+// Everything here is float32: the inputs r, k, v, z come out of their projections
+// unrounded, the decay, the state, the sums.  A token's sums run over i = 0 .. N-1 in
+// that order whatever the batch holds and however the prompt was cut, and the state is
+// carried through the slot, so a position's result does not depend on the cutting.
+//
+// Three kernels:
+//   shift_mix   m_s = h + (h_prev - h) * mu_s for s = 0 .. n_mix-1, h_prev being the row
+//               before in the same request, or the request's last row of the step before
+//               (kept in its state slot, zeros at the start); the slot is updated.
+//   scan        the recurrence above over the rows of every request, one CTA per
+//               (head, request), thread j owning column j of S in registers.
+//   gate_norm   y = o / rms(o over the head's N values) * gain * silu(g).
+#include "common.cuh"
+
+KLLM_EXPORT_LAST_ERROR(wkv)
+
+namespace {
+
+// ---- token shift ---------------------------------------------------------------
+// grid: one CTA per token.  The thread of channel c of a request's FIRST row reads the
+// slot's channel c and afterwards writes the request's LAST row there; no other thread
+// touches that element, so a one-row request (decode) and a portion behave alike.
+template <typename T>
+__global__ void __launch_bounds__(256)
+shift_mix_kernel(T* __restrict__ out, const T* __restrict__ h, const float* __restrict__ mu, float* __restrict__ state,
+                 int64_t state_stride, int64_t prev_off, const int* __restrict__ q_start,
+                 const int* __restrict__ token_req, const int* __restrict__ state_slots, int n, int d, int n_mix) {
+    griddep_wait();
+    griddep_launch();
+    const int t = blockIdx.x;
+    const int s = token_req[t];
+    const int first_row = q_start[s];
+    const bool first = t == first_row;
+    float* slot = state + (int64_t)state_slots[s] * state_stride + prev_off;
+    const T* hr = h + (int64_t)t * d;
+    const T* pr = h + (int64_t)(t - 1) * d;
+    const T* last = h + (int64_t)(q_start[s + 1] - 1) * d;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+        const float x = to_f32(hr[c]);
+        float p;
+        if (first) {
+            p = slot[c];
+            slot[c] = to_f32(last[c]);
+        } else {
+            p = to_f32(pr[c]);
+        }
+        const float diff = p - x;
+        for (int m = 0; m < n_mix; m++)
+            out[((int64_t)m * n + t) * d + c] = from_f32<T>(x + diff * mu[(int64_t)m * d + c]);
+    }
+}
+
+// ---- the recurrence --------------------------------------------------------------
+// blockDim = N rounded up to a warp; thread j < N owns S[0..N-1][j].  The r, k, w, u*k of a
+// token are shared through shared memory (two buffers: the next token's values are
+// loaded and its decay computed while this token's sums run).
+template <int NMAX>
+__global__ void __launch_bounds__(NMAX)
+wkv_scan_kernel(float* __restrict__ o, int64_t o_stride, const float* __restrict__ r, int64_t r_stride,
+                const float* __restrict__ k, int64_t k_stride, const float* __restrict__ v, int64_t v_stride,
+                const float* __restrict__ z, int64_t z_stride, const float* __restrict__ w0,
+                const float* __restrict__ u, float* __restrict__ state, int64_t state_stride,
+                const int* __restrict__ q_start, const int* __restrict__ state_slots, int N) {
+    __shared__ float sh[2][4][NMAX];          // r, k, w, u * k
+    griddep_wait();
+    griddep_launch();
+    const int head = blockIdx.x, s = blockIdx.y, j = threadIdx.x;
+    const int t0 = q_start[s], t1 = q_start[s + 1];
+    if (t0 >= t1) return;
+    const bool on = j < N;
+    const int64_t col = (int64_t)head * N + j;
+    float* S_g = state + (int64_t)state_slots[s] * state_stride + (int64_t)head * N * N;
+    float S[NMAX];
+#pragma unroll
+    for (int i = 0; i < NMAX; i++) S[i] = (on && i < N) ? S_g[(int64_t)i * N + j] : 0.f;
+    const float w0j = on ? w0[col] : 0.f, uj = on ? u[col] : 0.f;
+
+    auto stage = [&](int t, int buf) {
+        if (on) {
+            const float kk = k[(int64_t)t * k_stride + col];
+            sh[buf][0][j] = r[(int64_t)t * r_stride + col];
+            sh[buf][1][j] = kk;
+            sh[buf][2][j] = expf(-expf(z[(int64_t)t * z_stride + col] + w0j));
+            sh[buf][3][j] = uj * kk;
+        }
+    };
+    stage(t0, 0);
+    float vj = on ? v[(int64_t)t0 * v_stride + col] : 0.f;
+    __syncthreads();
+    for (int t = t0; t < t1; t++) {
+        const int buf = (t - t0) & 1;
+        float v_next = 0.f;
+        if (t + 1 < t1) {
+            stage(t + 1, buf ^ 1);
+            v_next = on ? v[(int64_t)(t + 1) * v_stride + col] : 0.f;
+        }
+        float acc = 0.f;
+#pragma unroll
+        for (int i = 0; i < NMAX; i++) {
+            if (i < N) {
+                const float a = sh[buf][1][i] * vj;
+                acc += sh[buf][0][i] * (S[i] + sh[buf][3][i] * vj);
+                S[i] = sh[buf][2][i] * S[i] + a;
+            }
+        }
+        if (on) o[(int64_t)t * o_stride + col] = acc;
+        vj = v_next;
+        __syncthreads();
+    }
+    if (on) {
+#pragma unroll
+        for (int i = 0; i < NMAX; i++)
+            if (i < N) S_g[(int64_t)i * N + j] = S[i];
+    }
+}
+
+// ---- output: unit norm per head, gain, gate ---------------------------------------------
+// one warp per (token, head); lane l adds the squares of its channels l, l + 32, ... in that
+// order, then the lanes in a fixed tree.
+template <typename T>
+__global__ void __launch_bounds__(256)
+gate_norm_kernel(T* __restrict__ y, const float* __restrict__ o, int64_t o_stride, const float* __restrict__ g,
+                 int64_t g_stride, const float* __restrict__ gain, int64_t rows, int heads, int N, float eps) {
+    griddep_wait();
+    griddep_launch();
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const int64_t t = row / heads;
+    const int head = (int)(row - t * heads);
+    const float* orow = o + t * o_stride + (int64_t)head * N;
+    const float* grow = g + t * g_stride + (int64_t)head * N;
+    float ss = 0.f;
+    for (int c = lane; c < N; c += 32) ss += orow[c] * orow[c];
+    ss = warp_sum(ss);
+    const float scale = rsqrtf(ss / (float)N + eps);
+    T* yrow = y + (t * heads + head) * N;
+    for (int c = lane; c < N; c += 32) {
+        const float gv = grow[c];
+        yrow[c] = from_f32<T>(orow[c] * scale * gain[(int64_t)head * N + c] * (gv / (1.f + expf(-gv))));
+    }
+}
+
+}  // namespace
+
+// out [n_mix][n][d] and h [n][d] in the element type `dtype`; mu float32 [n_mix][d]; the previous
+// row of request s lives at state[state_slots[s] * state_stride + prev_off .. + d].
+extern "C" int kllm_wkv_shift_mix(void* out, const void* h, const float* mu, float* state, int64_t state_stride,
+                                  int64_t prev_off, const int* q_start, const int* token_req, const int* state_slots,
+                                  int n, int d, int n_mix, int dtype, void* stream) {
+    if (n <= 0) return 0;
+    if (d <= 0 || n_mix <= 0) KLLM_FAIL("wkv shift: width %d, %d mixes", d, n_mix);
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = d >= 1024 ? 256 : 128;
+    if (dtype == KLLM_F32)
+        kllm_launch((shift_mix_kernel<float>), dim3(n), dim3(threads), 0, s, (float*)out, (const float*)h, mu, state,
+                    state_stride, prev_off, q_start, token_req, state_slots, n, d, n_mix);
+    else if (dtype == KLLM_BF16)
+        kllm_launch((shift_mix_kernel<bf16>), dim3(n), dim3(threads), 0, s, (bf16*)out, (const bf16*)h, mu, state,
+                    state_stride, prev_off, q_start, token_req, state_slots, n, d, n_mix);
+    else
+        KLLM_FAIL("wkv shift: unknown element type %d", dtype);
+    KLLM_LAUNCH_STATUS();
+}
+
+// o, r, k, v, z float32 with `heads * N` dense columns and their own row strides; w0, u float32
+// [heads * N]; the state of request s is state[state_slots[s] * state_stride ..], [heads][N][N].
+extern "C" int kllm_wkv_scan(float* o, int64_t o_stride, const float* r, int64_t r_stride, const float* k,
+                             int64_t k_stride, const float* v, int64_t v_stride, const float* z, int64_t z_stride,
+                             const float* w0, const float* u, float* state, int64_t state_stride, const int* q_start,
+                             const int* state_slots, int n_requests, int heads, int N, void* stream) {
+    if (n_requests <= 0) return 0;
+    if (heads <= 0 || N <= 0 || N > 128) KLLM_FAIL("wkv scan: %d heads of size %d (a head holds up to 128 channels)", heads, N);
+    if (n_requests > 65535) KLLM_FAIL("wkv scan: %d requests in one launch", n_requests);
+    cudaStream_t s = (cudaStream_t)stream;
+#define KLLM_WKV(NMAX)                                                                                                  \
+    kllm_launch((wkv_scan_kernel<NMAX>), dim3(heads, n_requests), dim3(NMAX), 0, s, o, o_stride, r, r_stride, k, k_stride, \
+                v, v_stride, z, z_stride, w0, u, state, state_stride, q_start, state_slots, N)
+    if (N <= 32) KLLM_WKV(32);
+    else if (N <= 64) KLLM_WKV(64);
+    else if (N <= 96) KLLM_WKV(96);
+    else KLLM_WKV(128);
+#undef KLLM_WKV
+    KLLM_LAUNCH_STATUS();
+}
+
+// y [n][heads * N] contiguous in the element type `dtype`; o and g (the gate before its
+// activation) float32 with their own row strides; gain float32 [heads * N].
+extern "C" int kllm_wkv_gate_norm(void* y, const float* o, int64_t o_stride, const float* g, int64_t g_stride,
+                                  const float* gain, int n, int heads, int N, float eps, int dtype, void* stream) {
+    if (n <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int64_t rows = (int64_t)n * heads;
+    const dim3 grid((unsigned)((rows + 7) / 8));
+    if (dtype == KLLM_F32)
+        kllm_launch((gate_norm_kernel<float>), grid, dim3(256), 0, s, (float*)y, o, o_stride, g, g_stride, gain, rows, heads, N, eps);
+    else if (dtype == KLLM_BF16)
+        kllm_launch((gate_norm_kernel<bf16>), grid, dim3(256), 0, s, (bf16*)y, o, o_stride, g, g_stride, gain, rows, heads, N, eps);
+    else
+        KLLM_FAIL("wkv gate: unknown element type %d", dtype);
+    KLLM_LAUNCH_STATUS();
+}

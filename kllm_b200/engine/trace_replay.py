@@ -3,6 +3,7 @@ logits.  It samples nothing.  It drives the engine's own model, step function,
 cache manager and kernels, the ones that generation uses.
 
     trace_run --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N [--trace FILE]
+              [--page-size P] [--max-requests R]
 
 Steps come on standard input (or from ``--trace FILE``), one JSON object a line:
 
@@ -18,8 +19,8 @@ reader takes, engine/npy/npy.go:22-82, and its dumps use, tools/gen_reference.py
 When the input ends ``<out>/index.json`` lists every written row: step, row, request
 id and the row's position in its request.  After every step a line ``done <step>`` is
 printed and flushed.  The cache pool is sized for
-``--max-tokens`` tokens (each request's count rounded up to whole pages), so pages
-are used again.  The reference checks logits step by step in a Go test
+``--max-tokens`` tokens (each request's count rounded up to whole pages) and the engine
+has ``--max-requests`` state slots (4), so pages and slots are used again.  The reference checks logits step by step in a Go test
 (engine/oracle/oracle.go:47-137); it has no program that writes them.
 """
 from __future__ import annotations
@@ -38,6 +39,7 @@ def main(argv=None) -> int:
     ap.add_argument("--out", required=True)
     ap.add_argument("--max-tokens", type=int, required=True)
     ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--max-requests", type=int, default=4, help="requests that may be live at a time (state slots)")
     ap.add_argument("--device", type=int, default=0)
     ap.add_argument("--trace", default="", help="read the steps from this file instead of standard input")
     args = ap.parse_args(argv)
@@ -58,7 +60,7 @@ def main(argv=None) -> int:
     pages = -(-args.max_tokens // args.page_size)
     eng = Engine(args.model, Options(device=args.device, dtype=args.dtype, max_seq=max_pos,
                                      block_size=args.page_size, num_blocks=pages,
-                                     max_step_tokens=max(args.max_tokens, 1), max_batch=8))
+                                     max_step_tokens=max(args.max_tokens, 1), max_batch=max(1, args.max_requests)))
     live = {}
     held = {}       # request id -> tokens fed so far (the position of its next token)
     index = []

@@ -62,8 +62,8 @@ def _i32(t: Optional[torch.Tensor], what: str):
 
 
 def embed(out_x: torch.Tensor, table: torch.Tensor, ids: torch.Tensor,
-          last_token: Optional[torch.Tensor] = None) -> None:
-    """out_x[t,:] = float32(table[ids[t],:]); out_x float32 [n, d].  With ``last_token``
+          last_token: Optional[torch.Tensor] = None, scale: float = 1.0) -> None:
+    """out_x[t,:] = float32(table[ids[t],:]) * scale; out_x float32 [n, d].  With ``last_token``
     (int32, one entry per request slot) an id -(s + 1) means last_token[s], the token
     that ``sample`` stored there."""
     _cuda(out_x, table, ids, last_token)
@@ -74,8 +74,8 @@ def embed(out_x: torch.Tensor, table: torch.Tensor, ids: torch.Tensor,
     if table.shape[1] != d or ids.numel() != n:
         raise KernelError("embed: shapes do not agree")
     lib = load_library("embedding")
-    rc = lib.kllm_embed(_p(out_x), _p(table), _p(ids), _p(last_token), n, d, table.shape[0], dtype_code(table.dtype),
-                        _stream())
+    rc = lib.kllm_embed(_p(out_x), _p(table), _p(ids), _p(last_token), n, d, table.shape[0], ctypes.c_float(scale),
+                        dtype_code(table.dtype), _stream())
     _check(lib, "embedding", rc)
 
 
@@ -117,6 +117,63 @@ def add_rmsnorm(x: torch.Tensor, res: Optional[torch.Tensor], out: torch.Tensor,
                               ctypes.c_float(eps), dtype_code(out.dtype),
                               dtype_code(res.dtype if res is not None else out.dtype), _stream())
     _check(lib, "norm", rc)
+
+
+def rmsnorm_add(x: torch.Tensor, y: torch.Tensor, gain: torch.Tensor, eps: float,
+                out: Optional[torch.Tensor] = None, gain2: Optional[torch.Tensor] = None, eps2: float = 0.0) -> None:
+    """x += rmsnorm(y) * gain, all float32 [n, d]: a norm on a sublayer's output as it joins
+    the residual stream.  With ``out`` [n, d] (model dtype) and ``gain2`` also
+    out = rmsnorm(x) * gain2 of the updated rows, the norm in front of the next sublayer."""
+    _cuda(x, y, gain, out, gain2)
+    d = x.shape[1]
+    for t in (x, y):
+        if t.dtype != torch.float32 or not t.is_contiguous() or t.shape != x.shape:
+            raise KernelError("rmsnorm_add: x and y must be contiguous float32 of one shape")
+    if gain.dtype != torch.float32 or gain.numel() != d:
+        raise KernelError("rmsnorm_add: gain must be float32 [d]")
+    if out is not None and (gain2 is None or gain2.dtype != torch.float32 or gain2.numel() != d
+                            or not out.is_contiguous() or out.shape != x.shape):
+        raise KernelError("rmsnorm_add: the second norm needs a float32 gain [d] and a contiguous out like x")
+    lib = load_library("norm")
+    rc = lib.kllm_rmsnorm_add(_p(x), _p(y), _p(gain), ctypes.c_float(eps), _p(out), _p(gain2), ctypes.c_float(eps2),
+                              x.shape[0], d, dtype_code(out.dtype if out is not None else torch.float32), _stream())
+    _check(lib, "norm", rc)
+
+
+def qknorm_append(q_out: torch.Tensor, qkv: torch.Tensor, q_gain: torch.Tensor, k_gain: Optional[torch.Tensor],
+                  eps: float, temp_coef: float, temp_every: int, positions: torch.Tensor, token_req: torch.Tensor,
+                  block_table: Optional[torch.Tensor], kcache: Optional[torch.Tensor], vcache: Optional[torch.Tensor],
+                  n_heads: int, n_kv: int, head_dim: int, v_head_dim: int) -> None:
+    """RMS norm of the whole query projection and of the whole key projection (float32
+    ``qkv`` [n, H*dk + G*dk + G*dv]), the queries' temperature 1 + coef * ln(floor((p + 1) /
+    every) + 1), q stored in ``q_out`` [n, H*dk] (model dtype) and k, v written to the paged
+    caches [pages, G, page_size, dk] / [pages, G, page_size, dv] (csrc/qknorm_append.cu).
+    With ``kcache`` None ``qkv`` holds queries only and nothing is stored."""
+    _cuda(q_out, qkv, q_gain, k_gain, positions, token_req, block_table, kcache, vcache)
+    _i32(positions, "positions"); _i32(token_req, "token_req"); _i32(block_table, "block_table")
+    n = qkv.shape[0]
+    Q, K, V = n_heads * head_dim, n_kv * head_dim, n_kv * v_head_dim
+    if qkv.dtype != torch.float32 or qkv.stride(1) != 1 or qkv.shape[1] != (Q + K + V if kcache is not None else Q):
+        raise KernelError("qknorm_append: the projections must be float32 [n, q + k + v] with dense rows")
+    if q_out.shape != (n, Q) or not q_out.is_contiguous():
+        raise KernelError("qknorm_append: q_out must be contiguous [n, heads * head_dim]")
+    if q_gain.dtype != torch.float32 or q_gain.numel() != Q:
+        raise KernelError("qknorm_append: the query gain must be float32 [heads * head_dim]")
+    page_size = max_blocks = 0
+    if kcache is not None:
+        if k_gain is None or k_gain.dtype != torch.float32 or k_gain.numel() != K:
+            raise KernelError("qknorm_append: the key gain must be float32 [kv heads * head_dim]")
+        page_size, max_blocks = kcache.shape[2], block_table.shape[1]
+        if (kcache.dtype != q_out.dtype or vcache.dtype != q_out.dtype or not kcache.is_contiguous()
+                or not vcache.is_contiguous() or tuple(kcache.shape[1:]) != (n_kv, page_size, head_dim)
+                or tuple(vcache.shape[1:]) != (n_kv, page_size, v_head_dim) or vcache.shape[0] != kcache.shape[0]):
+            raise KernelError("qknorm_append: caches must be [pages, kv heads, page_size, size] in q_out's dtype")
+    lib = load_library("qknorm_append")
+    rc = lib.kllm_qknorm_append(_p(q_out), _p(qkv), ctypes.c_int64(qkv.stride(0)), _p(q_gain), _p(k_gain),
+                                ctypes.c_float(eps), ctypes.c_float(temp_coef), int(temp_every or 1), _p(positions),
+                                _p(token_req), _p(block_table), max_blocks, _p(kcache), _p(vcache), n, n_heads, n_kv,
+                                head_dim, v_head_dim, page_size, dtype_code(q_out.dtype), _stream())
+    _check(lib, "qknorm_append", rc)
 
 
 def rope_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cos_sin: Optional[torch.Tensor],
@@ -177,22 +234,26 @@ SIMT_CHUNK = 256      # keys per CTA when a decoding token's context is cut (att
 
 def attention_simt(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, ctx,
                    block_table: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, window: int,
-                   scale: float, score_slopes: Optional[torch.Tensor] = None) -> None:
+                   scale: float, score_slopes: Optional[torch.Tensor] = None, v_head_dim: Optional[int] = None) -> None:
     """Causal GQA attention of the step's tokens on the CUDA cores, float32 arithmetic
     (csrc/attention_simt.cu): the attention of the float32 path.  The requests that bring
     one token each at the head of the batch (decoding requests, which the scheduler puts
     first) have their contexts cut into chunks of SIMT_CHUNK keys, one CTA each, merged in
     chunk order; the portions after them run as tiles of up to 64 (token, head) rows.
     ``score_slopes`` (float32 [n_heads]): slope[h] * (key position - query position) is added
-    to the scaled scores of head h."""
+    to the scaled scores of head h.  ``v_head_dim``: the size of a head's values and of its
+    output where it differs from the keys' (``vcache`` [pages, n_kv, page_size, v_head_dim],
+    ``out`` [n, n_heads * v_head_dim])."""
     _cuda(out, q, kcache, vcache, block_table, score_slopes)
+    vd = int(v_head_dim or head_dim)
     if score_slopes is not None and (score_slopes.dtype != torch.float32 or not score_slopes.is_contiguous()
                                      or score_slopes.numel() != n_heads):
         raise KernelError("attention: score slopes must be a contiguous float32 tensor, one per head")
     _i32(block_table, "block_table"); _i32(ctx.q_start, "q_start"); _i32(ctx.start_pos, "start_pos")
     if q.stride(1) != 1 or not out.is_contiguous() or out.dtype != q.dtype or kcache.dtype != q.dtype:
         raise KernelError("attention: operands must share a dtype; out contiguous, q rows dense")
-    if not kcache.is_contiguous() or not vcache.is_contiguous() or kcache.shape[1] != n_kv or kcache.shape[3] != head_dim:
+    if not kcache.is_contiguous() or not vcache.is_contiguous() or kcache.shape[1] != n_kv or kcache.shape[3] != head_dim \
+            or vcache.shape[3] != vd or vcache.shape[:3] != kcache.shape[:3] or out.shape[1] != n_heads * vd:
         raise KernelError("attention: cache layout must be [pages, n_kv, page_size, head_dim]")
     group = n_heads // max(1, n_kv)
     lib = load_library("attention_simt")
@@ -205,11 +266,11 @@ def attention_simt(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vca
     if window:
         bound = min(bound, int(window))
     splits = max(1, -(-bound // SIMT_CHUNK))
-    common = (n_heads, n_kv, head_dim, kcache.shape[2], int(window or 0), ctypes.c_float(scale))
+    common = (n_heads, n_kv, head_dim, vd, kcache.shape[2], int(window or 0), ctypes.c_float(scale))
     first = 0
     global launches
     if singles and splits > 1:
-        part_o = torch.empty((singles * n_heads, splits, head_dim), dtype=torch.float32, device=q.device)
+        part_o = torch.empty((singles * n_heads, splits, vd), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((singles * n_heads, splits, 2), dtype=torch.float32, device=q.device)
         rc = lib.kllm_attention_simt(_p(out), _p(part_o), _p(part_ml), _p(q), ctypes.c_int64(q.stride(0)), _p(kcache),
                                      _p(vcache), _p(ctx.q_start), _p(ctx.start_pos), _p(block_table),
@@ -217,7 +278,7 @@ def attention_simt(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vca
                                      _p(score_slopes), dtype_code(q.dtype), _stream())
         _check(lib, "attention_simt", rc)
         rc = lib.kllm_attention_simt_merge(_p(out), _p(part_o), _p(part_ml), _p(ctx.positions), singles, n_heads,
-                                           head_dim, int(window or 0), SIMT_CHUNK, splits, dtype_code(q.dtype), _stream())
+                                           vd, int(window or 0), SIMT_CHUNK, splits, dtype_code(q.dtype), _stream())
         _check(lib, "attention_simt", rc)
         first = singles
     if first < n_req:
@@ -230,11 +291,12 @@ def attention_simt(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vca
         _check(lib, "attention_simt", rc)
 
 
-def simt_fits(q: torch.Tensor, n_heads: int, n_kv: int, head_dim: int) -> bool:
-    """Whether ``attention_simt`` takes these operands: head size a multiple of 4 up to
-    256, at most 64 heads per kv head, rows aligned to four elements."""
+def simt_fits(q: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, v_head_dim: Optional[int] = None) -> bool:
+    """Whether ``attention_simt`` takes these operands: head sizes (keys, values) multiples of
+    4 up to 256, at most 64 heads per kv head, rows aligned to four elements."""
     quad = 4 * q.element_size()
-    return (head_dim % 4 == 0 and 0 < head_dim <= 256 and n_heads // max(1, n_kv) <= 64
+    vd = int(v_head_dim or head_dim)
+    return (head_dim % 4 == 0 and 0 < head_dim <= 256 and vd % 4 == 0 and 0 < vd <= 256 and n_heads // max(1, n_kv) <= 64
             and q.data_ptr() % quad == 0 and q.stride(0) % 4 == 0)
 
 
@@ -276,7 +338,8 @@ def decode_splits(n_tokens: int, n_kv: int, ctx_bound: int) -> int:
 
 def attention(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, ctx,
               block_table: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, window: int,
-              scale: float, score_slopes: Optional[torch.Tensor] = None) -> None:
+              scale: float, score_slopes: Optional[torch.Tensor] = None, v_head_dim: Optional[int] = None,
+              exact_weights: bool = False) -> None:
     """Causal GQA attention of the step's tokens over the paged cache, by the
     kernel that fits: bfloat16 with a head size in TC_HEAD_DIMS runs on tensor cores
     (the decode form when every request brings one token, else the prefill form: on
@@ -288,14 +351,19 @@ def attention(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: 
     over many CTAs, the portions after them the prefill form, in which a single token
     would walk its whole context with one CTA of 128 rows, 127 of them idle.
     ``score_slopes`` (a bias on the scores that is linear in the distance, per head) is
-    taken by the CUDA-core kernel only; the tensor-core kernels have no such argument."""
+    taken by the CUDA-core kernel only; the tensor-core kernels have no such argument.  So are
+    values of another size than the keys (``v_head_dim``) and ``exact_weights`` (the softmax
+    weights meet the values as float32 numbers; the tensor-core kernels round them to
+    bfloat16 for their second product)."""
     group = n_heads // max(1, n_kv)
-    if score_slopes is not None:
-        if not simt_fits(q, n_heads, n_kv, head_dim):
-            raise KernelError("attention: a bias on the scores needs a head size that is a multiple of 4 up to 256, "
-                              "at most 64 heads per kv head and rows aligned to four elements")
+    vd = int(v_head_dim or head_dim)
+    if score_slopes is not None or vd != head_dim or exact_weights:
+        if not simt_fits(q, n_heads, n_kv, head_dim, vd):
+            raise KernelError("attention: a bias on the scores, values of another size than the keys or float32 "
+                              "weights need head sizes that are multiples of 4 up to 256, at most 64 heads per kv "
+                              "head and rows aligned to four elements")
         return attention_simt(out, q, kcache, vcache, ctx, block_table, n_heads, n_kv, head_dim, window, scale,
-                              score_slopes)
+                              score_slopes, vd)
     tc = q.dtype == torch.bfloat16 and head_dim in TC_HEAD_DIMS
     if tc and ctx.all_single and group <= 16:
         return attention_decode(out, q, kcache, vcache, ctx.positions, ctx.token_req, block_table, n_heads,
@@ -804,3 +872,161 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = 
     if out is not None:
         return torch.mm(x, weight.t(), out=out)
     return torch.mm(x, weight.t())
+
+
+# ---- recurrent mixer (csrc/wkv.cu) ---------------------------------------------------
+
+def wkv_shift_mix(h: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, prev_off: int, ctx) -> torch.Tensor:
+    """[n_mix, n, d] = h + (h_prev - h) * mu[m]: h [n, d] in the model dtype, mu float32
+    [n_mix, d]; h_prev is the row before in the same request, for a request's first row of
+    the step what ``state[slot, prev_off : prev_off + d]`` holds, which is then replaced by the
+    request's last row."""
+    _cuda(h, mu, state)
+    n, d = h.shape
+    if not h.is_contiguous() or mu.dtype != torch.float32 or not mu.is_contiguous() or mu.shape[1] != d:
+        raise KernelError("wkv_shift_mix: h contiguous [n, d], mu float32 [mixes, d]")
+    if state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1 or prev_off + d > state.shape[1]:
+        raise KernelError("wkv_shift_mix: the state must be float32 [slots, size] with room for a row at prev_off")
+    out = torch.empty((mu.shape[0], n, d), dtype=h.dtype, device=h.device)
+    lib = load_library("wkv")
+    rc = lib.kllm_wkv_shift_mix(_p(out), _p(h), _p(mu), _p(state), ctypes.c_int64(state.stride(0)),
+                                ctypes.c_int64(prev_off), _p(ctx.q_start), _p(ctx.token_req), _p(ctx.state_slots), n, d,
+                                mu.shape[0], dtype_code(h.dtype), _stream())
+    _check(lib, "wkv", rc)
+    return out
+
+
+def _f32_rows(t: torch.Tensor, cols: int, what: str):
+    if t.dtype != torch.float32 or t.dim() != 2 or t.stride(1) != 1 or t.shape[1] != cols:
+        raise KernelError(f"{what} must be float32 [n, {cols}] with dense rows")
+
+
+def wkv_scan(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor, w0: torch.Tensor, u: torch.Tensor,
+             state: torch.Tensor, ctx, heads: int, size: int) -> torch.Tensor:
+    """The recurrence o_j = sum_i r_i (S_ij + u_i k_i v_j), S_ij <- w_i S_ij + k_i v_j with
+    w = exp(-exp(z + w0)), per head over every request's rows in order; S [heads, size, size]
+    is the head of ``state[slot]`` (float32) and is carried on.  All operands float32."""
+    _cuda(r, k, v, z, w0, u, state)
+    A = heads * size
+    for t, what in ((r, "r"), (k, "k"), (v, "v"), (z, "z")):
+        _f32_rows(t, A, "wkv_scan: " + what)
+    if w0.dtype != torch.float32 or u.dtype != torch.float32 or w0.numel() != A or u.numel() != A \
+            or not w0.is_contiguous() or not u.is_contiguous():
+        raise KernelError("wkv_scan: w0 and u must be contiguous float32 [heads * size]")
+    if state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1 or state.shape[1] < A * size:
+        raise KernelError("wkv_scan: the state must be float32 [slots, >= heads * size * size]")
+    o = torch.empty((r.shape[0], A), dtype=torch.float32, device=r.device)
+    lib = load_library("wkv")
+    rc = lib.kllm_wkv_scan(_p(o), ctypes.c_int64(o.stride(0)), _p(r), ctypes.c_int64(r.stride(0)), _p(k),
+                           ctypes.c_int64(k.stride(0)), _p(v), ctypes.c_int64(v.stride(0)), _p(z),
+                           ctypes.c_int64(z.stride(0)), _p(w0), _p(u), _p(state), ctypes.c_int64(state.stride(0)),
+                           _p(ctx.q_start), _p(ctx.state_slots), ctx.n_requests, heads, size, _stream())
+    _check(lib, "wkv", rc)
+    return o
+
+
+def wkv_gate_norm(o: torch.Tensor, g: torch.Tensor, gain: torch.Tensor, eps: float, heads: int, size: int,
+                  dtype: torch.dtype) -> torch.Tensor:
+    """y = o / rms(o over each head's ``size`` values) * gain * silu(g), stored in ``dtype``."""
+    _cuda(o, g, gain)
+    A = heads * size
+    _f32_rows(o, A, "wkv_gate_norm: o"); _f32_rows(g, A, "wkv_gate_norm: g")
+    if gain.dtype != torch.float32 or gain.numel() != A or not gain.is_contiguous():
+        raise KernelError("wkv_gate_norm: gain must be contiguous float32 [heads * size]")
+    y = torch.empty((o.shape[0], A), dtype=dtype, device=o.device)
+    lib = load_library("wkv")
+    rc = lib.kllm_wkv_gate_norm(_p(y), _p(o), ctypes.c_int64(o.stride(0)), _p(g), ctypes.c_int64(g.stride(0)), _p(gain),
+                                o.shape[0], heads, size, ctypes.c_float(eps), dtype_code(dtype), _stream())
+    _check(lib, "wkv", rc)
+    return y
+
+
+_UNARY = {"relu2": 0, "tanh": 1}
+
+
+def unary(x: torch.Tensor, op: str, dtype: torch.dtype) -> torch.Tensor:
+    """f(x) elementwise of a float32 matrix with dense rows, stored in ``dtype``; ``op``:
+    "relu2" (the square of relu) or "tanh"."""
+    _cuda(x)
+    if x.dtype != torch.float32 or x.dim() != 2 or x.stride(1) != 1:
+        raise KernelError("unary: the input must be a float32 matrix with dense rows")
+    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    lib = load_library("activation")
+    rc = lib.kllm_unary(_p(out), ctypes.c_int64(out.stride(0)), _p(x), ctypes.c_int64(x.stride(0)), x.shape[0],
+                        x.shape[1], _UNARY[op], dtype_code(dtype), _stream())
+    _check(lib, "activation", rc)
+    return out
+
+
+# ---- routed experts (csrc/moe.cu) ------------------------------------------------------
+
+def moe_route(h: torch.Tensor, router: torch.Tensor, top: int, score: str = "sigmoid", renormalize: bool = False):
+    """(idx int32 [n, top], weights float32 [n, top]): logits router @ h in float32, scores by
+    ``score`` ("sigmoid" or "softmax"), the ``top`` largest, the lower index among equals."""
+    _cuda(h, router)
+    n, d = h.shape
+    if not h.is_contiguous() or router.dtype != torch.float32 or not router.is_contiguous() or router.shape[1] != d:
+        raise KernelError("moe_route: h contiguous [n, d], router float32 [experts, d]")
+    if score not in ("sigmoid", "softmax"):
+        raise KernelError(f"moe_route: unknown score {score!r}")
+    idx = torch.empty((n, top), dtype=torch.int32, device=h.device)
+    wt = torch.empty((n, top), dtype=torch.float32, device=h.device)
+    lib = load_library("moe")
+    rc = lib.kllm_moe_route(_p(idx), _p(wt), _p(h), _p(router), n, d, router.shape[0], int(top),
+                            int(score == "softmax"), int(bool(renormalize)), dtype_code(h.dtype), _stream())
+    _check(lib, "moe", rc)
+    return idx, wt
+
+
+def moe_sort(idx: torch.Tensor, experts: int):
+    """(offsets int32 [experts + 1], perm int32 [rows]): the flattened (token, choice) pairs
+    ordered by expert; sorted row r is pair perm[r], expert e owns rows offsets[e] ..
+    offsets[e + 1]."""
+    _cuda(idx)
+    _i32(idx, "idx")
+    rows = idx.numel()
+    offsets = torch.empty(experts + 1, dtype=torch.int32, device=idx.device)
+    perm = torch.empty(rows, dtype=torch.int32, device=idx.device)
+    rank = torch.empty(rows, dtype=torch.int32, device=idx.device)
+    lib = load_library("moe")
+    rc = lib.kllm_moe_sort(_p(offsets), _p(perm), _p(rank), _p(idx), rows, int(experts), _stream())
+    _check(lib, "moe", rc)
+    return offsets, perm
+
+
+def moe_gemm(a: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, perm: torch.Tensor, wt: torch.Tensor, top: int,
+             gated: bool, scale_in: bool = False, scale_out: bool = False) -> torch.Tensor:
+    """The experts' products over rows sorted by expert (``moe_sort``).  ``gated``: a is the
+    layer's input [tokens, K], w [E, 2N, K] (gate rows, then up rows); returns silu(gate) * up
+    [rows, N] in a's dtype, sorted order, the input row times its weight when ``scale_in``.
+    Otherwise a is [rows, K] in sorted order, w [E, N, K]; returns float32 [rows, N] with row
+    token * top + choice, times its weight when ``scale_out``."""
+    _cuda(a, w, offsets, perm, wt)
+    _i32(offsets, "offsets"); _i32(perm, "perm")
+    rows = perm.numel()
+    E, N, K = w.shape
+    if gated:
+        N //= 2
+    if a.dtype != w.dtype or a.stride(1) != 1 or a.shape[1] != K or not w.is_contiguous():
+        raise KernelError("moe_gemm: a [., K] with dense rows and w [E, ., K] contiguous, of one dtype")
+    if wt.dtype != torch.float32 or not wt.is_contiguous() or wt.numel() != rows:
+        raise KernelError("moe_gemm: one float32 weight per (token, choice)")
+    c = torch.empty((rows, N), dtype=a.dtype if gated else torch.float32, device=a.device)
+    lib = load_library("moe")
+    rc = lib.kllm_moe_gemm(_p(c), _p(a), ctypes.c_int64(a.stride(0)), _p(w), _p(offsets), _p(perm), _p(wt), rows, E,
+                           int(top), N, K, int(gated), int(scale_in), int(scale_out), dtype_code(a.dtype), _stream())
+    _check(lib, "moe", rc)
+    return c
+
+
+def moe_combine(parts: torch.Tensor, top: int) -> torch.Tensor:
+    """y[t] = sum of parts[t * top + j] over j in order; float32."""
+    _cuda(parts)
+    if top == 1:
+        return parts
+    n, d = parts.shape[0] // top, parts.shape[1]
+    y = torch.empty((n, d), dtype=torch.float32, device=parts.device)
+    lib = load_library("moe")
+    rc = lib.kllm_moe_combine(_p(y), _p(parts), n, d, int(top), _stream())
+    _check(lib, "moe", rc)
+    return y

@@ -6,4 +6,4 @@ __all__ = ["LayerCache", "StepContext", "BlockSpec", "BuildEnv", "LayerCall", "M
            "PagedKVNeed", "PartSpec", "StateNeed", "TensorSpec", "part_factory", "register_part"]
 
 # the built-in part kinds register themselves on import
-from . import attention, block, embedding, mlp, norm, rotary  # noqa: E402,F401
+from . import attention, block, embedding, mlp, moe, norm, qk_norm, rotary, wkv  # noqa: E402,F401

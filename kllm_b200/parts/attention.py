@@ -13,9 +13,16 @@ and attention kernels, since the fused kernel rotates the raw projections itself
 ``score_slopes`` (a list of one float per head, None for Llama: slope[h] * (key
 position - query position) is added to the scaled scores, the form of position
 encodings that act on the scores; such a layer runs the CUDA-core attention kernel, the
-only one that takes the argument).
+only one that takes the argument), ``v_head_dim`` (the size of a head's values and of its
+output where it differs from ``head_dim``; same kernel), ``exact_weights`` (True: the softmax
+weights stay float32 until they have met the values; same kernel), ``tensors`` (a dict
+q/k/v/o -> full tensor names where they are not ``<prefix>.{q,k,v,o}_proj.weight``).
+A ``qk_transform`` that offers ``prepare(qkv, ctx, cache, attention) -> q`` is given the
+float32 result of the stacked projection instead: it returns the queries in the model dtype
+and writes keys and values into the cache itself (one kernel between the product and the
+attention, as the rotary kernel is for Llama); it needs ``position`` None.
 Tensors: ``<prefix>.{q,k,v,o}_proj.weight`` with shapes [H*hd, d], [G*hd, d],
-[G*hd, d], [d, H*hd]; no bias (reference backend/model.cu:1090-1104).  At bind time
+[G*vd, d], [d, H*vd]; no bias (reference backend/model.cu:1090-1104).  At bind time
 q, k and v are stacked into one [(H+2G)*hd, d] matrix so the three projections are
 one product.
 
@@ -54,15 +61,26 @@ class PagedAttention:
             raise ValueError(f"{self.n_heads} heads are not a multiple of {self.n_kv} kv heads")
         self.window = p.get("window")
         self.scale = float(p.get("scale") or 1.0 / math.sqrt(self.head_dim))
+        self.v_head_dim = int(p.get("v_head_dim") or self.head_dim)
+        self.exact_weights = bool(p.get("exact_weights", False))
         self.q_dim = self.n_heads * self.head_dim
         self.kv_dim = self.n_kv * self.head_dim
+        self.v_dim = self.n_kv * self.v_head_dim
+        self.o_dim = self.n_heads * self.v_head_dim
         self.prefix = spec.prefix
+        self.names = dict(p.get("tensors") or {})
         self.dtype = env.dtype
         pos = p.get("position")
         self.position = part_factory("position", pos.kind)(pos, env) if pos is not None else None
         qt = p.get("qk_transform")
         self.qk_transform = part_factory("qk_transform", qt.kind)(qt, env) if qt is not None else None
+        self._prepares = hasattr(self.qk_transform, "prepare")
+        if self._prepares and pos is not None:
+            raise ValueError("attention: a qk_transform that stores keys and values goes without a position part")
         slopes = p.get("score_slopes")
+        if slopes == "geometric":
+            # the slopes 2^(-8 (h + 1) / H) of a bias that grows with the distance, head by head
+            slopes = [2.0 ** (-8.0 * (h + 1) / self.n_heads) for h in range(self.n_heads)]
         if slopes is not None and len(slopes) != self.n_heads:
             raise ValueError(f"score_slopes: {len(slopes)} values for {self.n_heads} heads")
         self.score_slopes = None if slopes is None else torch.tensor([float(v) for v in slopes], dtype=torch.float32,
@@ -77,14 +95,14 @@ class PagedAttention:
         self._after = []           # weights streamed right after this part (see set_prefetch_targets)
 
     def _names(self):
-        return {k: f"{self.prefix}.{k}_proj.weight" for k in "qkvo"}
+        return {k: self.names.get(k) or f"{self.prefix}.{k}_proj.weight" for k in "qkvo"}
 
     def tensor_specs(self):
         n = self._names()
         return [TensorSpec(n["q"], (self.q_dim, self.hidden)),
                 TensorSpec(n["k"], (self.kv_dim, self.hidden)),
-                TensorSpec(n["v"], (self.kv_dim, self.hidden)),
-                TensorSpec(n["o"], (self.hidden, self.q_dim))] + \
+                TensorSpec(n["v"], (self.v_dim, self.hidden)),
+                TensorSpec(n["o"], (self.hidden, self.o_dim))] + \
             (self.position.tensor_specs() if self.position else []) + \
             (self.qk_transform.tensor_specs() if self.qk_transform else [])
 
@@ -98,12 +116,16 @@ class PagedAttention:
             self.qk_transform.bind(tensors)
 
     def cache_need(self):
-        return PagedKVNeed(self.n_kv, self.head_dim, self.window)
+        return PagedKVNeed(self.n_kv, self.head_dim, self.window,
+                           None if self.v_head_dim == self.head_dim else self.v_head_dim)
 
     def _split(self, qkv, writes):
         q = qkv[:, :self.q_dim]
         if not writes:
             return q, q, q
+        if self.v_head_dim != self.head_dim:
+            raise ValueError("attention: values of another size than the keys need a qk_transform that stores them "
+                             "(the rotary kernels write keys and values of one size)")
         return q, qkv[:, self.q_dim:self.q_dim + self.kv_dim], qkv[:, self.q_dim + self.kv_dim:]
 
     def streamed_weights(self):
@@ -119,6 +141,16 @@ class PagedAttention:
     def _target(self, i):
         return self._after[i] if i < len(self._after) else None
 
+    def _attend_prepared(self, qkv, ctx, cache):
+        """The route of a ``qk_transform`` with ``prepare``: it takes the float32 projections,
+        returns q and has stored k and v."""
+        q = self.qk_transform.prepare(qkv, ctx, cache, self)
+        attn = torch.empty((q.shape[0], self.o_dim), dtype=self.dtype, device=q.device)
+        kernels.attention(attn, q, cache.k, cache.v, ctx, cache.block_table, self.n_heads, self.n_kv,
+                          self.head_dim, self.window or 0, self.scale, score_slopes=self.score_slopes,
+                          v_head_dim=self.v_head_dim, exact_weights=self.exact_weights)
+        return attn
+
     def _attend(self, q, k, v, ctx, cache, prefetch=None):
         n = q.shape[0]
         group = self.n_heads // self.n_kv
@@ -126,8 +158,8 @@ class PagedAttention:
         if self.qk_transform is not None:
             self.qk_transform.apply(q, k if cache.writes else None, ctx, self.n_heads, self.n_kv, self.head_dim)
             table = None          # the fused decode kernel takes the raw projections
-        if self.score_slopes is not None:
-            table = None          # ... and has no bias on its scores
+        if self.score_slopes is not None or self.v_head_dim != self.head_dim or self.exact_weights:
+            table = None          # ... and has no bias on its scores, one head size, bfloat16 weights
         if (table is not None and cache.writes and ctx.all_single and self.dtype == torch.bfloat16 and group <= 16
                 and self.head_dim in kernels.TC_HEAD_DIMS and self.head_dim % 32 == 0):
             # decode: rotary encoding, cache write and attention in one kernel
@@ -146,14 +178,18 @@ class PagedAttention:
         elif cache.writes:
             kernels.rope_append(q, k, v, None, ctx.positions, ctx.token_req, cache.block_table,
                                 cache.k, cache.v, self.n_heads, self.n_kv, self.head_dim)
-        attn = torch.empty((n, self.q_dim), dtype=self.dtype, device=q.device)
+        attn = torch.empty((n, self.o_dim), dtype=self.dtype, device=q.device)
         kernels.attention(attn, q, cache.k, cache.v, ctx, cache.block_table, self.n_heads, self.n_kv,
-                          self.head_dim, self.window or 0, self.scale, score_slopes=self.score_slopes)
+                          self.head_dim, self.window or 0, self.scale, score_slopes=self.score_slopes,
+                          v_head_dim=self.v_head_dim, exact_weights=self.exact_weights)
         return attn
 
     def forward(self, xn, ctx, cache):
         # a layer that reads another layer's cache projects its queries only
         w = self.w_qkv if cache.writes else self.w_qkv[:self.q_dim]
+        if self._prepares:
+            attn = self._attend_prepared(kernels.linear(xn, w, out_dtype=torch.float32), ctx, cache)
+            return kernels.linear(attn, self.w_o, out_dtype=torch.float32)
         q, k, v = self._split(kernels.linear(xn, w), cache.writes)
         attn = self._attend(q, k, v, ctx, cache)
         # float32 out: the result goes into the residual stream unrounded
@@ -161,6 +197,8 @@ class PagedAttention:
 
     def forward_residual(self, x, norm, ctx, cache):
         n = x.shape[0]
+        if self._prepares:
+            return False
         w = self.w_qkv if cache.writes else self.w_qkv[:self.q_dim]
         if not (getattr(norm, "fusable_rmsnorm", False) and kernels.skinny_fits(n, self.hidden, self.dtype)
                 and kernels.skinny_fits(n, self.q_dim, self.dtype, sliced=True)):

@@ -75,4 +75,54 @@ class PreNormBlock:
         return self.feed_forward.forward(xn, ctx)
 
 
+class SandwichNormBlock:
+    """``sandwich_norm``: a norm before AND after each sublayer,
+
+        x += post1(mixer(pre1(x)));  x += post2(ff(pre2(x)))
+
+    ``BlockSpec.mixer_norm`` / ``ff_norm`` are the norms in front; ``params`` holds
+    ``mixer_post_norm`` and ``ff_post_norm`` (PartSpecs of the norm family whose parts offer
+    ``add_normed``).  ``feed_forward`` may be None: the layer is its mixer alone.  The
+    sublayers' outputs are float32; the norm behind the mixer and the norm in front of the
+    feed-forward are one kernel.  Nothing is ever pending."""
+
+    def __init__(self, spec: BlockSpec, env: BuildEnv):
+        def norm(ps):
+            return part_factory("norm", ps.kind)(ps, env)
+        self.mixer = part_factory("mixer", spec.mixer.kind)(spec.mixer, env)
+        self.mixer_norm = norm(spec.mixer_norm)
+        self.mixer_post = norm(spec.params["mixer_post_norm"])
+        self.feed_forward = self.ff_norm = self.ff_post = None
+        if spec.feed_forward is not None:
+            self.feed_forward = part_factory("feed_forward", spec.feed_forward.kind)(spec.feed_forward, env)
+            self.ff_norm = norm(spec.ff_norm)
+            self.ff_post = norm(spec.params["ff_post_norm"])
+
+    def parts(self):
+        return [p for p in (self.mixer_norm, self.mixer, self.mixer_post, self.ff_norm, self.feed_forward, self.ff_post)
+                if p is not None]
+
+    def tensor_specs(self):
+        return [s for p in self.parts() for s in p.tensor_specs()]
+
+    @property
+    def graph_safe(self):
+        return all(getattr(p, "graph_safe", True) for p in self.parts())
+
+    def bind(self, tensors):
+        for p in self.parts():
+            p.bind(tensors)
+
+    def forward(self, x, pending, ctx, cache):
+        xn = self.mixer_norm.forward(x, pending)
+        y = self.mixer.forward(xn, ctx, cache)
+        if self.feed_forward is None:
+            self.mixer_post.add_normed(x, y)
+            return None
+        xn = self.mixer_post.add_normed(x, y, then=self.ff_norm)
+        self.ff_post.add_normed(x, self.feed_forward.forward(xn, ctx))
+        return None
+
+
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "sandwich_norm", SandwichNormBlock)

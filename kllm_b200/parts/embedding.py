@@ -1,11 +1,12 @@
 """Token embedding and output head.
 
-Embedding: params ``vocab``, ``width``; tensor ``<prefix>.weight`` [vocab, width];
-``forward(ids) -> x`` float32 [n, width], the residual stream (reference
-backend/model.cu:89-95, no scaling for Llama).
+Embedding: params ``vocab``, ``width``, optional ``scale`` (every row is multiplied by it,
+default 1) and ``tensor`` (the table's full name where it is not ``<prefix>.weight``); tensor
+``<prefix>.weight`` [vocab, width]; ``forward(ids) -> x`` float32 [n, width], the residual
+stream (reference backend/model.cu:89-95, no scaling for Llama).
 
 Head: params ``vocab``, ``width``, ``tied_to`` (name of the embedding tensor to
-share, or None); tensor ``<prefix>.weight`` [vocab, width] unless tied;
+share, or None), optional ``tensor`` (full name); tensor ``<prefix>.weight`` [vocab, width] unless tied;
 ``forward(xn) -> logits`` float32 [rows, vocab], accumulated in float32 (reference
 backend/model.cu:1187; tying resolved offline there, tools/convert_hf.py:81-82).
 """
@@ -21,7 +22,8 @@ class TokenEmbedding:
     def __init__(self, spec: PartSpec, env: BuildEnv):
         self.vocab = int(spec.params["vocab"])
         self.width = int(spec.params["width"])
-        self.name = spec.prefix + ".weight"
+        self.scale = float(spec.params.get("scale", 1.0))
+        self.name = spec.params.get("tensor") or spec.prefix + ".weight"
         self.table = None
 
     def tensor_specs(self):
@@ -32,7 +34,7 @@ class TokenEmbedding:
 
     def forward(self, ids, last_token=None):
         x = torch.empty((ids.numel(), self.width), dtype=torch.float32, device=ids.device)
-        kernels.embed(x, self.table, ids, last_token)
+        kernels.embed(x, self.table, ids, last_token, self.scale)
         return x
 
 
@@ -41,7 +43,7 @@ class LinearHead:
         self.vocab = int(spec.params["vocab"])
         self.width = int(spec.params["width"])
         self.tied_to = spec.params.get("tied_to")
-        self.name = spec.prefix + ".weight"
+        self.name = spec.params.get("tensor") or spec.prefix + ".weight"
         self.weight = None
 
     def tensor_specs(self):

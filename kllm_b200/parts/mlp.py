@@ -95,4 +95,34 @@ class GatedMLP:
         return True
 
 
+class PlainMLP:
+    """Feed-forward without a gate: down(act(up x)).  params: ``hidden``, ``intermediate``,
+    ``activation`` ("relu2": the square of relu), optional ``tensors`` (up/down -> full
+    names; default ``<prefix>.up`` and ``<prefix>.down``).  The up product's float32 result
+    meets the activation unrounded; the result is float32 [n, hidden]."""
+
+    def __init__(self, spec: PartSpec, env: BuildEnv):
+        p = spec.params
+        self.hidden = int(p["hidden"])
+        self.inter = int(p["intermediate"])
+        self.activation = p.get("activation", "relu2")
+        if self.activation not in ("relu2",):
+            raise ValueError(f"plain feed-forward: activation {self.activation!r} has no kernel (relu2 only)")
+        names = dict(p.get("tensors") or {})
+        self.up_name = names.get("up") or f"{spec.prefix}.up"
+        self.down_name = names.get("down") or f"{spec.prefix}.down"
+        self.dtype = env.dtype
+
+    def tensor_specs(self):
+        return [TensorSpec(self.up_name, (self.inter, self.hidden)), TensorSpec(self.down_name, (self.hidden, self.inter))]
+
+    def bind(self, tensors):
+        self.w_up, self.w_down = tensors[self.up_name], tensors[self.down_name]
+
+    def forward(self, xn, ctx):
+        act = kernels.unary(kernels.linear(xn, self.w_up, out_dtype=torch.float32), self.activation, self.dtype)
+        return kernels.linear(act, self.w_down, out_dtype=torch.float32)
+
+
 register_part("feed_forward", "gated_mlp", GatedMLP)
+register_part("feed_forward", "plain_mlp", PlainMLP)

@@ -14,7 +14,7 @@ from typing import Dict, List, Optional
 import torch
 
 # registering the built-in part kinds
-from . import attention, block, embedding, mlp, norm, rotary  # noqa: F401
+from . import attention, block, embedding, mlp, moe, norm, qk_norm, rotary, wkv  # noqa: F401
 from .context import LayerCache, StepContext
 from .spec import BuildEnv, ModelSpec, PagedKVNeed, StateNeed, TensorSpec, part_factory
 
@@ -32,6 +32,7 @@ class DecoderModel:
         self.final_norm = part_factory("norm", spec.final_norm.kind)(spec.final_norm, env)
         self.head = part_factory("head", spec.head.kind)(spec.head, env)
         self.schedule = list(spec.schedule)
+        self.tap = None         # debugging: tap(i, x) is called with the residual stream after schedule entry i
         self._check_schedule()
 
     def _check_schedule(self):
@@ -71,7 +72,7 @@ class DecoderModel:
         """False when a part says that its forward cannot be captured into a CUDA graph
         (class or instance attribute ``graph_safe = False``: it reads device data on the
         host, or its shapes depend on the data)."""
-        return all(getattr(p, "graph_safe", True) for p in self.parts())
+        return self.tap is None and all(getattr(p, "graph_safe", True) for p in self.parts())
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         for p in self.parts():
@@ -100,12 +101,14 @@ class DecoderModel:
         is wanted; the cache is still filled)."""
         x = self.embedding.forward(ctx.token_ids, ctx.last_token)
         pending = None
-        for call in self.schedule:
+        for i, call in enumerate(self.schedule):
             cache = caches[call.cache]
             if cache.writes != call.writes_cache:
                 cache = LayerCache(cache.k, cache.v, cache.block_table, cache.state,
                                    writes=call.writes_cache, page_size=cache.page_size)
             pending = self.blocks[call.block].forward(x, pending, ctx, cache)
+            if self.tap is not None:
+                self.tap(i, x if pending is None else x + pending)
         if ctx.n_want == 0:
             return None
         if pending is None and hasattr(self.head, "forward_normed"):

@@ -1,12 +1,16 @@
 """RMSNorm with the residual sum folded in.
 
-params: ``width``, ``eps``.  Tensor: ``<prefix>.weight`` [width], kept in float32
+params: ``width``, ``eps``, optional ``tensor`` (the gain's full name where it is not
+``<prefix>.weight``).  Tensor: ``<prefix>.weight`` [width], kept in float32
 (reference backend/model.cu:101-122, 144-165; the gain is used as stored, no 1 + w).
 Interface of a norm part:
 ``forward(x, res, rows=None) -> out``: x is the float32 residual stream [n, width];
 ``res`` (float32 or model dtype, or None) is added into x first and x is written back; the
 result is in the model dtype.  With ``rows`` only those rows are normalised and x
 is left as it is.
+``add_normed(x, y, then=None)``: x += rmsnorm(y) * gain for a float32 sublayer output y, the
+form of a norm that sits AFTER a sublayer; with ``then`` (another norm of this kind) it also
+returns that norm of the updated x, computed in the same kernel.
 
 A part that can apply this norm inside its own kernel (see ``forward_residual`` of
 the attention and feed-forward parts) recognises it by ``fusable_rmsnorm`` and
@@ -26,7 +30,7 @@ class RMSNorm:
     def __init__(self, spec: PartSpec, env: BuildEnv):
         self.width = int(spec.params["width"])
         self.eps = float(spec.params["eps"])
-        self.name = spec.prefix + ".weight"
+        self.name = spec.params.get("tensor") or spec.prefix + ".weight"
         self.dtype = env.dtype
         self.gain = None
 
@@ -40,6 +44,15 @@ class RMSNorm:
         n = x.shape[0] if rows is None else rows.numel()
         out = torch.empty((n, self.width), dtype=self.dtype, device=x.device)
         kernels.add_rmsnorm(x, res, out, self.gain, self.eps, rows=rows)
+        return out
+
+
+    def add_normed(self, x, y, then=None):
+        if then is None:
+            kernels.rmsnorm_add(x, y, self.gain, self.eps)
+            return None
+        out = torch.empty(x.shape, dtype=self.dtype, device=x.device)
+        kernels.rmsnorm_add(x, y, self.gain, self.eps, out=out, gain2=then.gain, eps2=then.eps)
         return out
 
 

@@ -25,15 +25,24 @@ class TensorSpec:
     store: "compute" -> kept in the model's dtype (bfloat16 or float32);
            "float32" -> kept in 32-bit whatever the model's dtype (norm gains,
            router tables); "int32" -> integer table.
-    init:  how random-weights mode fills it: "normal" (mean 0), "gain" (mean 1) or
-           "zeros"; the spreads are arguments of that mode.
+    init:  how random-weights mode fills it: "normal" (mean 0), "gain" (mean 1),
+           "zeros", or "uniform:lo:hi"; the spreads are arguments of that mode.
     optional: may be absent from the files (the part then copes, e.g. a tied head).
+    free:  indices of dimensions whose size the files decide (a rank that no configuration
+           key names); ``shape`` then holds the size that random-weights mode draws, and the
+           part reads the real one from the tensor it is bound to.
     """
     name: str
     shape: Tuple[int, ...]
     store: str = "compute"
     init: str = "normal"
     optional: bool = False
+    free: Tuple[int, ...] = ()
+
+    def fits(self, shape) -> bool:
+        shape = tuple(shape)
+        return len(shape) == len(self.shape) and all(
+            a == b or (i in self.free and a > 0) for i, (a, b) in enumerate(zip(shape, self.shape)))
 
 
 @dataclass
@@ -49,9 +58,9 @@ class BlockSpec:
     kind: str
     prefix: str
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]     # None where the arrangement allows a layer without one
     mixer_norm: PartSpec
-    ff_norm: PartSpec
+    ff_norm: Optional[PartSpec]
     params: Dict = field(default_factory=dict)
 
 
@@ -80,10 +89,16 @@ class ModelSpec:
 @dataclass(frozen=True)
 class PagedKVNeed:
     """Keys and values in pages.  window None: every key is kept; window W: only
-    the last W keys of a request are ever read, older pages may be given back."""
+    the last W keys of a request are ever read, older pages may be given back.
+    v_head_dim: the size of a head's values where it differs from the keys' (None: the same)."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_head_dim: Optional[int] = None
+
+    @property
+    def value_dim(self) -> int:
+        return self.v_head_dim or self.head_dim
 
 
 @dataclass(frozen=True)

@@ -73,7 +73,7 @@ def check_names(files: ModelFiles, specs: Iterable[TensorSpec], model_dir: str, 
     wrong_shape, wrong_dtype = [], []
     for name in sorted(have & set(by_name)):
         e = files.entry(name)
-        if tuple(e.shape) != tuple(by_name[name].shape):
+        if not by_name[name].fits(e.shape):
             wrong_shape.append((name, tuple(e.shape), tuple(by_name[name].shape)))
         ok = _INTS if by_name[name].store == "int32" else _FLOATS
         if e.dtype not in ok:

@@ -40,7 +40,10 @@ def random_tensor(spec, seed: int, std: float, gain_std: float, dtype: torch.dty
     if spec.store == "int32":
         raise ValueError(f"random-weights mode cannot fill the integer table {spec.name}")
     t = torch.randn(spec.shape, generator=g, dtype=torch.float32, device=device)
-    if spec.init == "gain":
+    if spec.init.startswith("uniform:"):
+        lo, hi = (float(v) for v in spec.init.split(":")[1:])
+        t = lo + (hi - lo) * torch.rand(spec.shape, generator=g, dtype=torch.float32, device=device)
+    elif spec.init == "gain":
         t = 1.0 + gain_std * t
     elif spec.init == "normal":
         t = std * t
