@@ -37,6 +37,11 @@ printed in the same form but not the bench line; their weights are drawn on the 
 ``--workload llama2-7b-mixed`` runs BASELINE.json's continuous-batching workload (32
 requests, prompt lengths uniform in [128, 3072], 128 new tokens each) through the
 scheduler and prints a record of its own.
+``--design sozarax`` measures the Sozarax design (recurrent and biased-attention layers,
+dense and routed feed-forwards) at two layer sizes beside a Llama of the same width, depth,
+heads and feed-forward size: prefill and decode throughput of both models, and the design's
+own kernels one by one against their rooflines beside the Llama kernel that does the like
+work.  A record of its own; the default line does not change.
 """
 from __future__ import annotations
 
@@ -243,6 +248,9 @@ def main():
     ap.add_argument("--workload", default="", choices=["", "llama2-7b-mixed"],
                     help="llama2-7b-mixed: 32 requests, prompts uniform in [128, 3072], 128 new tokens each, through "
                          "the scheduler (a record of its own, not the bench line)")
+    ap.add_argument("--design", default="", choices=["", "sozarax"],
+                    help="sozarax: prefill and decode of that design at two layer sizes beside a Llama of equal size, and "
+                         "its kernels against their rooflines (a record of its own, not the bench line)")
     args = ap.parse_args()
     if args.timeline:
         os.environ["KLLM_B200_TIMELINE"] = "1"
@@ -264,6 +272,8 @@ def main():
 
     if args.workload:
         return mixed_workload(args)
+    if args.design:
+        return design_comparison(args)
     if args.only == "attention":
         return attention_forms()
     if args.only == "products":
@@ -597,6 +607,236 @@ def streaming_products(rows: int, dtype: str = "bfloat16"):
         out.append({"product": name, "us": round(us, 1), "tb_per_s": round(N * K * esize * mats / us / 1e6, 2)})
         del ws, w2
     print(json.dumps({"partial": f"weight-streaming products alone, {rows} rows, {dtype}", "rows": out}))
+    return 0
+
+
+def sozarax_config(width, layers, heads, kv_heads, head_dim, ff, experts, top, expert_ff, vocab):
+    """A Sozarax model of ``layers`` layers in the pattern recurrent + dense, attention + routed,
+    recurrent + dense, recurrent + routed; every head of either mixer has ``head_dim`` channels."""
+    wkv = {"heads": heads, "dim": head_dim}
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5,
+           "q_temp": {"coef": 0.3, "every": 128}}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top}}
+    pattern = [("wkv", wkv, dense), ("attention", att, moe), ("wkv", wkv, dense), ("wkv", wkv, moe)]
+    return {"architecture": "Sozarax", "vocab": vocab, "width": width, "embedding": {"scale": width ** 0.5},
+            "norm": {"eps": 1e-6},
+            "layers": [{"type": t, "mixer": dict(m), "mlp": dict(f)} for t, m, f in (pattern[i % 4] for i in range(layers))]}
+
+
+DESIGN_SIZES = {
+    # name: width, layers, heads, kv heads, head size, dense ff, experts, top, expert ff, vocabulary
+    "2048-wide": (2048, 8, 32, 4, 64, 5632, 8, 2, 1408, 32000),
+    "4096-wide": (4096, 4, 32, 8, 128, 14336, 8, 2, 3584, 32000),
+}
+
+
+def design_comparison(args):
+    """Prefill and decode of the Sozarax design and of a Llama of equal size, and the design's
+    kernels alone.  Times by CUDA events on the launching stream after warm-up, medians of
+    repeats; inputs of the kernel measurements rotate over buffers larger than L2 in sum."""
+    import math
+    import torch
+    from kllm_b200 import kernels
+    from kllm_b200.engine import Engine, Options, StepEntry
+    pk = peaks()
+    dtype = args.dtype
+    tdt = torch.bfloat16 if dtype == "bfloat16" else torch.float32
+    T, B, ctx, page = args.prefill_tokens, args.batch, args.context, 64
+    g = torch.Generator().manual_seed(1)
+    sampler = ClockSampler(0)
+    t_begin = time.time()
+
+    def timed(fn, reps=5, inner=1):
+        out = []
+        for i in range(reps + 2):
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            ev0.record()
+            for _ in range(inner):
+                fn()
+            ev1.record()
+            torch.cuda.synchronize()
+            if i >= 2:
+                out.append(ev0.elapsed_time(ev1) / inner)
+        return median(out)
+
+    def model_run(cfg, vocab):
+        pages = max(B * (-(-ctx // page)), -(-T // page)) + 8
+        eng = Engine(None, Options(dtype=dtype, max_seq=max(ctx, T), block_size=page, num_blocks=pages, max_batch=B,
+                                   max_step_tokens=max(T, B)), config=cfg, random_seed=4)
+        ids = torch.randint(0, vocab, (T,), generator=g).tolist()
+
+        def prefill():
+            req = eng.cache.open()
+            eng.runner.run([StepEntry(req, ids, [T - 1])])
+            eng.cache.close(req)
+        ms_p = timed(prefill)
+        K = args.steps
+        reqs = [eng.cache.open() for _ in range(B)]
+        plen = ctx - (K * 7 + 8)
+        for r in reqs:
+            eng.runner.run([StepEntry(r, torch.randint(0, vocab, (plen,), generator=g).tolist(), [])])
+        tok = [1] * B
+
+        def decode():
+            eng.runner.run([StepEntry(r, [t], [0]) for r, t in zip(reqs, tok)])
+        for _ in range(3):
+            decode()
+        ms_d = timed(decode, reps=5, inner=K)
+        launches = eng.runner.graphs[B].launches if B in eng.runner.graphs else None
+        for r in reqs:
+            eng.cache.close(r)
+        eng.close()
+        del eng
+        torch.cuda.empty_cache()
+        return {"prefill_ms": round(ms_p, 3), "prefill_tok_s": round(T / ms_p * 1e3), "decode_ms_per_step": round(ms_d, 4),
+                "decode_tok_s": round(B / ms_d * 1e3), "kernels_per_decode_step": launches}
+
+    def rotate(make, bytes_each):
+        n = max(2, min(16, int(160e6 // max(1, bytes_each)) + 1))
+        return [make() for _ in range(n)]
+
+    def kernel_rows(width, heads, kv, hd, ff, E, top, eff):
+        rows = []
+        dev = "cuda"
+        f32 = torch.float32
+        A = heads * hd
+        hbm, tens = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+
+        def note(name, us, bytes_=0, flops=0, like=None, bound=None):
+            t_mem, t_flop = bytes_ / hbm * 1e6, flops / tens * 1e6
+            floor = max(t_mem, t_flop)
+            rows.append({"kernel": name, "us": round(us, 1), "floor_us": round(floor, 2),
+                         "bound": bound or ("memory" if t_mem >= t_flop else "tensor"),
+                         "times_floor": round(us / floor, 1) if floor > 0 else None, "like": like})
+
+        def ctx_of(n_new, start):
+            S = len(n_new)
+            import itertools
+            import types
+            qs = torch.tensor([0] + list(itertools.accumulate(n_new)), dtype=torch.int32, device=dev)
+            return types.SimpleNamespace(
+                n_tokens=sum(n_new), n_requests=S, q_start=qs,
+                token_req=torch.repeat_interleave(torch.arange(S, dtype=torch.int32), torch.tensor(n_new)).to(dev),
+                start_pos=torch.tensor(start, dtype=torch.int32, device=dev),
+                positions=torch.cat([torch.arange(s, s + c, dtype=torch.int32) for s, c in zip(start, n_new)]).to(dev),
+                state_slots=torch.arange(S, dtype=torch.int32, device=dev), host_n_new=list(n_new),
+                host_start_pos=list(start), all_single=all(c == 1 for c in n_new),
+                max_ctx=max(s + c for s, c in zip(start, n_new)), split_bound=0, max_new=max(n_new))
+
+        # ---- the recurrence: a prompt (one request of T rows) and a decode step (B requests of one row) ----
+        for name, n_new, start in (("wkv_scan prefill", [T], [0]), ("wkv_scan decode", [1] * B, [ctx - 1] * B)):
+            c = ctx_of(n_new, start)
+            n = sum(n_new)
+            sets = rotate(lambda: [torch.randn(n, A, device=dev) * 0.1 for _ in range(3)] + [torch.randn(n, A, device=dev) - 3],
+                          16 * n * A)
+            states = rotate(lambda: torch.zeros(len(n_new), A * hd + width, device=dev), 4 * len(n_new) * A * hd)
+            w0, u = torch.zeros(A, device=dev), torch.zeros(A, device=dev)
+            it = [0]
+
+            def call():
+                i = it[0] = it[0] + 1
+                r, k, v, z = sets[i % len(sets)]
+                kernels.wkv_scan(r, k, v, z, w0, u, states[i % len(states)], c, heads, hd)
+            us = timed(call, inner=4) * 1e3
+            # floor: the state read and written once, the rows read and written once; the sums themselves are
+            # float32 work of the CUDA cores (4 operations per state element and row), held against their peak
+            cores = 2 * 128 * kernels.sm_count() * 1.9e9
+            fl = 4.0 * n * A * hd
+            t_core = fl / cores * 1e6
+            by = 8.0 * len(n_new) * A * hd + 20.0 * n * A
+            rows.append({"kernel": name, "us": round(us, 1), "floor_us": round(max(by / hbm * 1e6, t_core), 2),
+                         "bound": "memory" if by / hbm * 1e6 >= t_core else "float32 cores",
+                         "times_floor": round(us / max(by / hbm * 1e6, t_core), 1),
+                         "like": "attention (the mixer's sequence step)"})
+            del sets, states
+        # ---- attention with the distance bias, and Llama's attention on the same cache ----
+        for name, n_new, start in (("attention prefill", [T], [0]), ("attention decode", [1] * B, [ctx - 1] * B)):
+            c = ctx_of(n_new, start)
+            n, S = sum(n_new), len(n_new)
+            per = -(-max(s + m for s, m in zip(start, n_new)) // page)
+            table = torch.arange(S * per, dtype=torch.int32, device=dev).view(S, per).contiguous()
+            caches = rotate(lambda: (torch.randn(S * per, kv, page, hd, device=dev).to(tdt),
+                                     torch.randn(S * per, kv, page, hd, device=dev).to(tdt)), 2 * S * per * kv * page * hd * 2)
+            q = (torch.randn(n, A, device=dev) * 0.2).to(tdt)
+            out = torch.empty_like(q)
+            slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / heads) for h in range(heads)], device=dev)
+            it = [0]
+            keys = sum((s + m) * m - m * (m - 1) // 2 for s, m in zip(start, n_new))     # visible (query, key) pairs
+            fl = 4.0 * keys * A
+            by = sum(s + m for s, m in zip(start, n_new)) * kv * hd * 2 * q.element_size() + 2 * n * A * q.element_size()
+            for biased in (True, False):
+                def call():
+                    i = it[0] = it[0] + 1
+                    kc, vc = caches[i % len(caches)]
+                    kernels.attention(out, q, kc, vc, c, table, heads, kv, hd, 0, hd ** -0.5,
+                                      score_slopes=slopes if biased else None, exact_weights=biased)
+                us = timed(call, inner=4) * 1e3
+                note(("biased " if biased else "llama ") + name, us, by, fl if dtype == "bfloat16" else 0,
+                     like=None if not biased else "llama " + name)
+            del caches
+        # ---- the experts' two products over a prompt and over a decode step, and Llama's dense products ----
+        for name, n in (("prefill", T), ("decode", B)):
+            x = (torch.randn(n, width, device=dev) * 0.5).to(tdt)
+            router = torch.randn(E, width, device=dev)
+            wsets = rotate(lambda: ((torch.randn(E, 2 * eff, width, device=dev) * 0.02).to(tdt),
+                                    (torch.randn(E, width, eff, device=dev) * 0.02).to(tdt)), 3 * E * eff * width * 2)
+            idx, wt = kernels.moe_route(x, router, top)
+            offsets, perm = kernels.moe_sort(idx, E)
+            it = [0]
+
+            def experts():
+                i = it[0] = it[0] + 1
+                gu, dn = wsets[i % len(wsets)]
+                act = kernels.moe_gemm(x, gu, offsets, perm, wt, top, gated=True, scale_in=True)
+                kernels.moe_combine(kernels.moe_gemm(act, dn, offsets, perm, wt, top, gated=False), top)
+            us = timed(experts, inner=2) * 1e3
+            used = min(E, n * top)
+            by = 3.0 * used * eff * width * x.element_size()
+            fl = 6.0 * n * top * eff * width
+            note(f"routed experts ({top} of {E}) {name}", us, by, fl if dtype == "bfloat16" else 0,
+                 like=f"llama gate/up/down {name}")
+            dsets = rotate(lambda: ((torch.randn(2 * ff, width, device=dev) * 0.02).to(tdt),
+                                    (torch.randn(width, ff, device=dev) * 0.02).to(tdt)), 3 * ff * width * 2)
+            resid = torch.zeros(n, width, device=dev)
+
+            def dense():
+                i = it[0] = it[0] + 1
+                gu, dn = dsets[i % len(dsets)]
+                if n <= 16 and dtype == "bfloat16":
+                    act = kernels.skinny_gemm(gu[:ff], weight_up=gu[ff:], x=x, epilogue="swiglu")
+                    kernels.skinny_gemm(dn, x=act, epilogue="add", out=resid)
+                else:
+                    y = kernels.linear(x, gu, out_dtype=f32)
+                    act = torch.empty(n, ff, dtype=tdt, device=dev)
+                    kernels.silu_mul(act, y[:, :ff], y[:, ff:])
+                    kernels.linear_add(resid, act, dn)
+            us = timed(dense, inner=2) * 1e3
+            note(f"llama gate/up/down {name}", us, 3.0 * ff * width * x.element_size(),
+                 6.0 * n * ff * width if dtype == "bfloat16" else 0)
+            del wsets, dsets
+        return rows
+
+    sizes = {}
+    for name, (width, layers, heads, kv, hd, ff, E, top, eff, vocab) in DESIGN_SIZES.items():
+        soz = sozarax_config(width, layers, heads, kv, hd, ff, E, top, eff, vocab)
+        llama = dict(TINYLLAMA, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads,
+                     num_key_value_heads=kv, head_dim=hd, intermediate_size=ff, vocab_size=vocab,
+                     max_position_embeddings=max(ctx, T))
+        print(f"[bench] {name}: Sozarax", file=sys.stderr, flush=True)
+        rec = {"layers": layers, "heads": heads, "kv_heads": kv, "head_dim": hd, "ff": ff,
+               "experts": f"{top} of {E} x {eff}", "sozarax": model_run(soz, vocab)}
+        print(f"[bench] {name}: Llama of equal size", file=sys.stderr, flush=True)
+        rec["llama"] = model_run(llama, vocab)
+        print(f"[bench] {name}: kernels", file=sys.stderr, flush=True)
+        rec["kernels"] = kernel_rows(width, heads, kv, hd, ff, E, top, eff)
+        sizes[name] = rec
+        torch.cuda.empty_cache()
+    sampler.stop()
+    print(json.dumps({"partial": "Sozarax beside a Llama of equal size", "dtype": dtype, "prefill_tokens": T,
+                      "decode_batch": B, "decode_context": ctx, "data": "synthetic, random weights",
+                      "peaks": pk, "clocks": sampler.summary(t_begin, time.time()), "sizes": sizes}))
     return 0
 
 

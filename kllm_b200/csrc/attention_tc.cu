@@ -182,7 +182,17 @@ struct DecodeFusion {
     int tl_slot;            // timeline row of this launch (-1: none)
     const void* prefetch;   // optional: weights that a later kernel streams, to be brought into L2
     long long prefetch_bytes;
+    // not part of the fusion, but carried here: a bias on the scores that is linear in the
+    // distance, slopes[head] * (key position - query position) after scaling (NULL: none;
+    // inv_scale = 1 / scale, the bias being added to the unscaled scores), and whether the
+    // probabilities meet the values as two bfloat16 terms (16 bits of mantissa) instead of one
+    const float* slopes;
+    float inv_scale;
+    int split_p;
 };
+
+// what rounding to bfloat16 leaves of x
+__device__ __forceinline__ float bf16_rest(float x) { return x - __bfloat162float(__float2bfloat16_rn(x)); }
 
 // Merge of the splits of one (token, kv head) by one CTA.  (m, l) of row r and split j
 // sit at ml + r * ml_r + j * ml_j, the partial output row at po + r * o_r + j * o_j, in
@@ -383,6 +393,8 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
 #pragma unroll
         for (int j = 0; j < 4; j++) o[i][j] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    const float sl0 = (fu.slopes && gid < gs) ? fu.slopes[g * gs + gid] * fu.inv_scale : 0.f;
+    const float sl1 = (fu.slopes && gid + 8 < gs) ? fu.slopes[g * gs + gid + 8] * fu.inv_scale : 0.f;
     TL_MARK(3);
 
     for (int i = 0; i < ntiles; i++) {
@@ -406,6 +418,13 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
         if (key_base < hi) {
             float s[2][4];
             scores16(s, qa, sk, warp, lane);
+            if (fu.slopes) {
+#pragma unroll
+                for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+                    for (int j = 0; j < 4; j++)
+                        s[nt][j] += (j < 2 ? sl0 : sl1) * (float)(key_base + nt * 8 + 2 * tq + (j & 1) - p_new);
+            }
 #pragma unroll
             for (int nt = 0; nt < 2; nt++)
 #pragma unroll
@@ -435,6 +454,11 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
             uint32_t pa[4] = {pack_bf16(p[0][0], p[0][1]), pack_bf16(p[0][2], p[0][3]),
                               pack_bf16(p[1][0], p[1][1]), pack_bf16(p[1][2], p[1][3])};
             accumulate16(o, pa, sv, warp, lane);
+            if (fu.split_p) {
+                uint32_t pl[4] = {pack_bf16(bf16_rest(p[0][0]), bf16_rest(p[0][1])), pack_bf16(bf16_rest(p[0][2]), bf16_rest(p[0][3])),
+                                  pack_bf16(bf16_rest(p[1][0]), bf16_rest(p[1][1])), pack_bf16(bf16_rest(p[1][2]), bf16_rest(p[1][3]))};
+                accumulate16(o, pl, sv, warp, lane);
+            }
         }
     }
     cp_async_wait<0>();
@@ -535,7 +559,8 @@ attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int64_t 
                     const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
                     const int* __restrict__ q_start, const int* __restrict__ start_pos,
                     const int* __restrict__ block_table, int max_blocks, int n_requests, int n_heads,
-                    int n_kv, int page_size, int window, float scale_log2e, int tokens_per_tile) {
+                    int n_kv, int page_size, int window, float scale_log2e, int tokens_per_tile,
+                    const float* __restrict__ slopes, float inv_scale, int split_p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* smem = reinterpret_cast<bf16*>(smem_raw);
     __shared__ int s_req, s_tok0;
@@ -572,6 +597,7 @@ attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int64_t 
     // this thread's rows, two per MMA tile: (token, head of the group)
     int pr[MT][2], wr[MT][2];            // position of the row's token (-1: row unused), first visible key
     bool vr[MT][2];
+    float sl_[MT][2];                    // the row's slope over the scale (0 without a bias)
     uint32_t qa[MT][KSTEPS][4];
     int64_t orow[MT][2];
 #pragma unroll
@@ -584,6 +610,7 @@ attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int64_t 
             vr[m][h] = tt < n_tok;
             pr[m][h] = vr[m][h] ? pos0 + tt : -1;
             wr[m][h] = (window > 0) ? pr[m][h] + 1 - window : 0;
+            sl_[m][h] = (slopes && vr[m][h]) ? slopes[g * gs + hh] * inv_scale : 0.f;
             qp[h] = q + (int64_t)(tok0 + tt) * q_stride + (int64_t)(g * gs + hh) * HD;
             orow[m][h] = (int64_t)(tok0 + tt) * n_heads * HD + (int64_t)(g * gs + hh) * HD;
         }
@@ -658,6 +685,16 @@ attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int64_t 
         uint32_t pa[MT][4][4];           // probabilities as bfloat16 A fragments, per 16-key slice
 #pragma unroll
         for (int m = 0; m < MT; m++) {
+            if (slopes) {
+#pragma unroll
+                for (int nt = 0; nt < 8; nt++)
+#pragma unroll
+                    for (int j = 0; j < 2; j++) {
+                        const int key = key0 + nt * 8 + 2 * tq + j;
+                        s[m][nt][j] += sl_[m][0] * (float)(key - pr[m][0]);
+                        s[m][nt][2 + j] += sl_[m][1] * (float)(key - pr[m][1]);
+                    }
+            }
             if (need_mask) {
 #pragma unroll
                 for (int nt = 0; nt < 8; nt++)
@@ -711,6 +748,16 @@ attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int64_t 
 #pragma unroll
         for (int sl = 0; sl < 4; sl++) {
             const bf16* base = sv + (16 * sl + (mi & 1) * 8 + (lane & 7)) * ROW + (mi >> 1) * 8;
+            uint32_t pl[MT][4];          // what the rounding of this slice's probabilities left
+            if (split_p) {
+#pragma unroll
+                for (int m = 0; m < MT; m++) {
+                    pl[m][0] = pack_bf16(bf16_rest(s[m][2 * sl][0]), bf16_rest(s[m][2 * sl][1]));
+                    pl[m][1] = pack_bf16(bf16_rest(s[m][2 * sl][2]), bf16_rest(s[m][2 * sl][3]));
+                    pl[m][2] = pack_bf16(bf16_rest(s[m][2 * sl + 1][0]), bf16_rest(s[m][2 * sl + 1][1]));
+                    pl[m][3] = pack_bf16(bf16_rest(s[m][2 * sl + 1][2]), bf16_rest(s[m][2 * sl + 1][3]));
+                }
+            }
 #pragma unroll
             for (int dp = 0; dp < HD / 16; dp++) {
                 uint32_t v[4];
@@ -719,6 +766,10 @@ attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int64_t 
                 for (int m = 0; m < MT; m++) {
                     mma_bf16(o[m][2 * dp], pa[m][sl], v[0], v[1]);
                     mma_bf16(o[m][2 * dp + 1], pa[m][sl], v[2], v[3]);
+                    if (split_p) {
+                        mma_bf16(o[m][2 * dp], pl[m], v[0], v[1]);
+                        mma_bf16(o[m][2 * dp + 1], pl[m], v[2], v[3]);
+                    }
                 }
             }
         }
@@ -783,12 +834,17 @@ extern "C" int kllm_attention_decode(void* out, void* part_o, void* part_ml, con
                                      const void* kcache, const void* vcache, const int* positions,
                                      const int* token_req, const int* block_table, int max_blocks,
                                      int n_tokens, int n_heads, int n_kv, int hd, int page_size, int window,
-                                     float scale, int num_splits, void* stream) {
+                                     float scale, int num_splits, const float* slopes, int split_p, void* stream) {
     if (n_tokens <= 0) return 0;
     int rc = check_common(n_heads, n_kv, hd, page_size, q, q_stride);
     if (rc) return rc;
     if (n_heads / n_kv > 16) KLLM_FAIL("attention decode: %d heads per kv head, at most 16", n_heads / n_kv);
     if (num_splits < 1 || (num_splits > 1 && (!part_o || !part_ml))) KLLM_FAIL("attention decode: bad split arguments");
+    if (slopes && !(scale > 0.f)) KLLM_FAIL("attention decode: a bias on the scores needs a positive scale");
+    DecodeFusion extra{};
+    extra.slopes = slopes;
+    extra.inv_scale = slopes ? 1.f / scale : 0.f;
+    extra.split_p = split_p;
     if (n_tokens > 65535 || n_kv > 65535) KLLM_FAIL("attention decode: grid too large");
     if ((rc = set_attributes())) return rc;
     cudaStream_t s = (cudaStream_t)stream;
@@ -801,13 +857,13 @@ extern "C" int kllm_attention_decode(void* out, void* part_o, void* part_ml, con
                     dec_smem_bytes(DEC_STAGES_DEEP), s, 
         (bf16*)out, (float*)part_o, (float*)part_ml, (const bf16*)q, q_stride, (bf16*)kcache,
         (bf16*)vcache, positions, token_req, block_table, max_blocks, n_heads, n_kv, page_size, window, sl2e,
-        num_splits, DecodeFusion{});
+        num_splits, extra);
     else
         kllm_launch((attn_decode_kernel<false, DEC_STAGES_WIDE>), dim3(grid), dim3(THREADS),
                     dec_smem_bytes(DEC_STAGES_WIDE), s, 
         (bf16*)out, (float*)part_o, (float*)part_ml, (const bf16*)q, q_stride, (bf16*)kcache,
         (bf16*)vcache, positions, token_req, block_table, max_blocks, n_heads, n_kv, page_size, window, sl2e,
-        num_splits, DecodeFusion{});
+        num_splits, extra);
     if (num_splits > 1)
         kllm_launch((attn_combine_kernel), dim3(n_tokens * n_heads), dim3(HD < 64 ? 32 : 64), 0, s, (bf16*)out, (const float*)part_o,
                                                                           (const float*)part_ml, num_splits);
@@ -842,7 +898,7 @@ extern "C" int kllm_attention_decode_fused(void* out, void* part_o, void* part_m
     if ((rc = set_attributes())) return rc;
     const float sl2e = scale * 1.4426950408889634f;
     DecodeFusion fu{(const bf16*)k_new, k_stride, (const bf16*)v_new, v_stride, cos_sin, (unsigned int*)counters, TL_SLOT(),
-                    prefetch, prefetch ? (long long)prefetch_bytes : 0LL};
+                    prefetch, prefetch ? (long long)prefetch_bytes : 0LL, nullptr, 0.f, 0};
     dim3 grid(num_splits, n_kv, n_tokens);
     const bool deep = (int64_t)num_splits * n_kv * n_tokens <= 2 * 148;
     auto go = [&](auto kernel, size_t smem) {
@@ -908,7 +964,7 @@ extern "C" int kllm_attention_decode_static(void* out, const void* q, int64_t q_
     }
     return kllm_attention_decode(out, part_o, part_ml, q, q_stride, kcache, vcache, positions, token_req,
                                  block_table, max_blocks, n_tokens, n_heads, n_kv, hd, page_size, window, scale,
-                                 num_splits, stream);
+                                 num_splits, nullptr, 0, stream);
 }
 
 // Prefill form: requests' portions q_start[s]..q_start[s+1] (prefix sums, [n_requests+1])
@@ -917,12 +973,13 @@ extern "C" int kllm_attention_prefill(void* out, const void* q, int64_t q_stride
                                       const void* vcache, const int* q_start, const int* start_pos,
                                       const int* block_table, int max_blocks, int n_tokens, int n_requests,
                                       int n_heads, int n_kv, int hd, int page_size, int window, float scale,
-                                      void* stream) {
+                                      const float* slopes, int split_p, void* stream) {
     if (n_tokens <= 0) return 0;
     int rc = check_common(n_heads, n_kv, hd, page_size, q, q_stride);
     if (rc) return rc;
     const int gs = n_heads / n_kv;
     if (gs > 64) KLLM_FAIL("attention prefill: %d heads per kv head, at most 64", gs);
+    if (slopes && !(scale > 0.f)) KLLM_FAIL("attention prefill: a bias on the scores needs a positive scale");
     if ((rc = set_attributes())) return rc;
     const int tpt = PRE_ROWS / gs;
     const int max_tiles = n_tokens / tpt + n_requests;          // >= sum of ceil(n_s / tpt)
@@ -930,6 +987,7 @@ extern "C" int kllm_attention_prefill(void* out, const void* q, int64_t q_stride
     dim3 grid(max_tiles * n_kv);
     kllm_launch((attn_prefill_kernel), dim3(grid), dim3(THREADS), PRE_SMEM_BYTES, (cudaStream_t)stream, 
         (bf16*)out, (const bf16*)q, q_stride, (const bf16*)kcache, (const bf16*)vcache, q_start, start_pos,
-        block_table, max_blocks, n_requests, n_heads, n_kv, page_size, window, sl2e, tpt);
+        block_table, max_blocks, n_requests, n_heads, n_kv, page_size, window, sl2e, tpt, slopes,
+        slopes ? 1.f / scale : 0.f, split_p);
     KLLM_LAUNCH_STATUS();
 }

@@ -6,8 +6,11 @@
 //   sort      the (token, choice) pairs ordered by expert: offsets[E + 1] and perm[n * top]
 //             (sorted row -> token * top + choice), on the device, so that a step's launch
 //             shapes do not depend on the routing.
-//   gemm      for the sorted rows of every expert e, C = A W_e^T as tiles of 32 rows x 64
-//             columns with float32 accumulation on the CUDA cores.  Two forms:
+//   gemm      for the sorted rows of every expert e, C = A W_e^T with float32 accumulation:
+//             bfloat16 operands as tiles of 64 rows x 64 columns on the tensor cores
+//             (mma.sync m16n8k16, operands through a three-stage cp.async ring), float32
+//             operands (and bfloat16 ones whose rows are not 16-byte aligned) as tiles of 32 x
+//             64 on the CUDA cores.  Two forms:
 //             "gated" reads row `token` of the layer's input, times the row's weight if the
 //             weight acts on the expert's input, and stores act(gate) * up per sorted row;
 //             "down" reads the sorted rows and stores row token * top + choice of a float32
@@ -43,18 +46,17 @@ route_kernel(int* __restrict__ idx, float* __restrict__ wt, const T* __restrict_
         if (lane == 0) z[e] = acc;
     }
     __syncwarp();
+    // the choice is made among the logits: both scores grow with them, and a sigmoid that has
+    // reached 1.0f no longer tells two experts apart
+    float zmax = 0.f, zsum = 1.f;
     if (softmax) {
-        float m = -INFINITY;
-        for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
-        m = warp_max(m);
-        float sum = 0.f;
-        for (int e = lane; e < E; e += 32) sum += expf(z[e] - m);
-        sum = warp_sum(sum);
-        for (int e = lane; e < E; e += 32) z[e] = expf(z[e] - m) / sum;
-    } else {
-        for (int e = lane; e < E; e += 32) z[e] = 1.f / (1.f + expf(-z[e]));
+        zmax = -INFINITY;
+        for (int e = lane; e < E; e += 32) zmax = fmaxf(zmax, z[e]);
+        zmax = warp_max(zmax);
+        zsum = 0.f;
+        for (int e = lane; e < E; e += 32) zsum += expf(z[e] - zmax);
+        zsum = warp_sum(zsum);
     }
-    __syncwarp();
     float total = 0.f;
     for (int c = 0; c < top; c++) {
         float best = -INFINITY;
@@ -67,12 +69,13 @@ route_kernel(int* __restrict__ idx, float* __restrict__ wt, const T* __restrict_
             const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
             if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
         }
+        const float score = softmax ? expf(best - zmax) / zsum : 1.f / (1.f + expf(-best));
         if (lane == 0) {
             idx[(int64_t)t * top + c] = bi;
-            wt[(int64_t)t * top + c] = best;
+            wt[(int64_t)t * top + c] = score;
             z[bi] = -INFINITY;
         }
-        total += best;
+        total += score;
         __syncwarp();
     }
     if (renorm && lane == 0)
@@ -203,6 +206,170 @@ expert_gemm_kernel(void* __restrict__ c_out, const T* __restrict__ a, int64_t a_
     }
 }
 
+// ---- the same on the tensor cores, bfloat16 ---------------------------------------------------
+// 128 threads; warp w owns rows 16 w .. 16 w + 15 of the tile and all 64 columns.  A weight on
+// the expert's input is applied to the accumulators instead: W (s x) = s (W x), the same
+// number without rounding s x to bfloat16 first.
+constexpr int TN = 64, TK = 64, TLD = TK + 8, TSTAGES = 3, TT = 128;
+
+__device__ __forceinline__ void cp16(bf16* dst, const bf16* src, bool ok) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    const int bytes = ok ? 16 : 0;                          // 0: filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void ldsm4(uint32_t (&r)[4], const bf16* p) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <bool GATED, int MW>
+constexpr size_t mma_smem_bytes() {
+    return (size_t)TSTAGES * (64 * MW + (GATED ? 2 : 1) * TN) * TLD * sizeof(bf16);
+}
+
+// MW: 16-row tiles per warp; a CTA's tile has TM = 64 * MW rows (128 where an expert has many
+// rows, so that a weight fragment serves two row tiles; 64 otherwise).
+template <bool GATED, int MW>
+__global__ void __launch_bounds__(TT)
+expert_gemm_mma_kernel(void* __restrict__ c_out, const bf16* __restrict__ a, int64_t a_stride, const bf16* __restrict__ w,
+                       const int* __restrict__ offsets, const int* __restrict__ perm, const float* __restrict__ wt,
+                       int E, int top, int N, int K, int scale_in, int scale_out) {
+    constexpr int NB = GATED ? 2 : 1, TM = 64 * MW;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16 (*As)[TM][TLD] = reinterpret_cast<bf16 (*)[TM][TLD]>(smem_raw);                           // [TSTAGES]
+    bf16 (*Bs)[NB][TN][TLD] = reinterpret_cast<bf16 (*)[NB][TN][TLD]>(smem_raw + (size_t)TSTAGES * TM * TLD * sizeof(bf16));
+    __shared__ int srow[TM];
+    __shared__ int sdst[TM];
+    __shared__ float sscale[TM];
+    griddep_wait();
+    griddep_launch();
+    int tile = blockIdx.y, e = 0, lo = 0, hi = 0;
+    for (; e < E; e++) {
+        lo = offsets[e];
+        hi = offsets[e + 1];
+        const int nt = (hi - lo + TM - 1) / TM;
+        if (tile < nt) break;
+        tile -= nt;
+    }
+    if (e >= E) return;
+    const int r0 = lo + tile * TM, nr = min(TM, hi - r0), n0 = blockIdx.x * TN;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gid = lane >> 2, tq = lane & 3;
+    for (int i = tid; i < TM; i += TT) {
+        int src = 0, dst = 0;
+        float sc = 1.f;
+        if (i < nr) {
+            const int flat = perm[r0 + i];
+            src = GATED ? flat / top : r0 + i;
+            dst = flat;
+            if (GATED ? scale_in : scale_out) sc = wt[flat];
+        }
+        srow[i] = src;
+        sdst[i] = dst;
+        sscale[i] = sc;
+    }
+    __syncthreads();
+    const bf16* we = w + (int64_t)e * NB * N * K;
+    auto load = [&](int stage, int k0) {
+        // rows x 8 chunks of 8 elements, for A and for each weight tile
+        for (int i = tid; i < TM * (TK / 8); i += TT) {
+            const int rr = i / (TK / 8), ch = (i % (TK / 8)) * 8;
+            const bool ok = rr < nr && k0 + ch < K;
+            cp16(&As[stage][rr][ch], a + (ok ? (int64_t)srow[rr] * a_stride + k0 + ch : 0), ok);
+        }
+#pragma unroll
+        for (int b = 0; b < NB; b++)
+            for (int i = tid; i < TN * (TK / 8); i += TT) {
+                const int cc = i / (TK / 8), ch = (i % (TK / 8)) * 8;
+                const bool ok = n0 + cc < N && k0 + ch < K;
+                cp16(&Bs[stage][b][cc][ch], we + (ok ? ((int64_t)b * N + n0 + cc) * K + k0 + ch : 0), ok);
+            }
+    };
+    float acc[NB][MW][8][4] = {};
+    const int nk = (K + TK - 1) / TK;
+#pragma unroll
+    for (int st = 0; st < TSTAGES - 1; st++) {
+        if (st < nk) load(st, st * TK);
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    }
+    for (int it = 0; it < nk; it++) {
+        asm volatile("cp.async.wait_group %0;\n" ::"n"(TSTAGES - 2) : "memory");
+        __syncthreads();
+        const int nxt = it + TSTAGES - 1;
+        if (nxt < nk) load(nxt % TSTAGES, nxt * TK);
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+        const int st = it % TSTAGES;
+        if (16 * MW * warp >= nr) continue;                 // none of this warp's rows exists
+#pragma unroll
+        for (int ks = 0; ks < TK / 16; ks++) {
+            uint32_t af[MW][4];
+#pragma unroll
+            for (int m = 0; m < MW; m++)
+                ldsm4(af[m], &As[st][16 * (MW * warp + m) + (lane & 15)][ks * 16 + (lane >> 4) * 8]);
+#pragma unroll
+            for (int b = 0; b < NB; b++)
+#pragma unroll
+                for (int np = 0; np < 4; np++) {
+                    uint32_t bfr[4];
+                    ldsm4(bfr, &Bs[st][b][16 * np + (lane >> 4) * 8 + (lane & 7)][ks * 16 + ((lane >> 3) & 1) * 8]);
+#pragma unroll
+                    for (int m = 0; m < MW; m++) {
+                        mma16816(acc[b][m][2 * np], af[m], bfr[0], bfr[1]);
+                        mma16816(acc[b][m][2 * np + 1], af[m], bfr[2], bfr[3]);
+                    }
+                }
+        }
+    }
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+#pragma unroll
+    for (int m = 0; m < MW; m++)
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int rr = 16 * (MW * warp + m) + gid + 8 * h;
+            if (rr >= nr) continue;
+            const float sc = sscale[rr];
+#pragma unroll
+            for (int nt = 0; nt < 8; nt++)
+#pragma unroll
+                for (int j = 0; j < 2; j++) {
+                    const int cc = n0 + nt * 8 + 2 * tq + j;
+                    if (cc >= N) continue;
+                    if (GATED) {
+                        const float gv = acc[0][m][nt][2 * h + j] * sc, uv = acc[NB - 1][m][nt][2 * h + j] * sc;
+                        ((bf16*)c_out)[(int64_t)(r0 + rr) * N + cc] = __float2bfloat16_rn(act_silu(gv) * uv);
+                    } else {
+                        ((float*)c_out)[(int64_t)sdst[rr] * N + cc] = acc[0][m][nt][2 * h + j] * sc;
+                    }
+                }
+        }
+}
+
+template <bool GATED, int MW>
+int launch_mma(void* c, const void* a, int64_t a_stride, const void* w, const int* offsets, const int* perm,
+               const float* wt, int rows, int E, int top, int N, int K, int scale_in, int scale_out, cudaStream_t s) {
+    auto kern = expert_gemm_mma_kernel<GATED, MW>;
+    static bool raised = false;
+    constexpr size_t smem = mma_smem_bytes<GATED, MW>();
+    if (!raised) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) {
+            snprintf(g_kllm_err, sizeof(g_kllm_err), "moe gemm: shared memory limit: %s", cudaGetErrorString(e));
+            return (int)e;
+        }
+        raised = true;
+    }
+    const int row_tiles = (rows + 64 * MW - 1) / (64 * MW) + E;
+    if (row_tiles > 65535) KLLM_FAIL("moe gemm: %d rows in one launch", rows);
+    kllm_launch(kern, dim3((N + TN - 1) / TN, row_tiles), dim3(TT), smem, s, c, (const bf16*)a, a_stride, (const bf16*)w,
+                offsets, perm, wt, E, top, N, K, scale_in, scale_out);
+    KLLM_LAUNCH_STATUS();
+}
+
 __global__ void __launch_bounds__(256)
 combine_kernel(float* __restrict__ y, const float* __restrict__ parts, int64_t total, int d, int top) {
     griddep_wait();
@@ -255,6 +422,18 @@ extern "C" int kllm_moe_gemm(void* c, const void* a, int64_t a_stride, const voi
     const int row_tiles = (rows + BM - 1) / BM + E;
     if (row_tiles > 65535) KLLM_FAIL("moe gemm: %d rows in one launch", rows);
     cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == KLLM_BF16 && K % 8 == 0 && a_stride % 8 == 0 && (((uintptr_t)a | (uintptr_t)w) & 15) == 0) {
+        // tiles of 128 rows where the experts have that many rows on average (which tile a row
+        // falls into changes no sum of that row)
+        const bool tall = rows / E >= 128;
+#define KLLM_MOE_MMA(G, MW) \
+    return launch_mma<G, MW>(c, a, a_stride, w, offsets, perm, wt, rows, E, top, N, K, scale_in, scale_out, s)
+        if (gated && tall) KLLM_MOE_MMA(true, 2);
+        if (gated) KLLM_MOE_MMA(true, 1);
+        if (tall) KLLM_MOE_MMA(false, 2);
+        KLLM_MOE_MMA(false, 1);
+#undef KLLM_MOE_MMA
+    }
     const dim3 grid((N + BN - 1) / BN, row_tiles);
 #define KLLM_MOE(T, G)                                                                                            \
     kllm_launch((expert_gemm_kernel<T, G>), grid, dim3(GT), 0, s, c, (const T*)a, a_stride, (const T*)w, offsets, perm, \

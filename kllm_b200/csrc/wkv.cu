@@ -18,8 +18,15 @@
 //   shift_mix   m_s = h + (h_prev - h) * mu_s for s = 0 .. n_mix-1, h_prev being the row
 //               before in the same request, or the request's last row of the step before
 //               (kept in its state slot, zeros at the start); the slot is updated.
-//   scan        the recurrence above over the rows of every request, one CTA per
-//               (head, request), thread j owning column j of S in registers.
+//   scan        the recurrence above over the rows of every request.  Heads of 16, 32, 64 or
+//               128 channels: a CTA per (head, slice of value channels, request); thread
+//               (j, g) keeps S[4g .. 4g+3][j] in registers, the N/4 threads of a value
+//               channel are neighbouring lanes and add their parts of o_j by shuffles in a
+//               fixed tree; r, k, the decay and u*k of four rows at a time are staged in
+//               shared memory (two buffers, one barrier per four rows).  Other head sizes
+//               up to 128: one CTA per (head, request), thread j owning all of S[.][j].
+//               In the slot the state lies as [heads][j][i], so a thread's part is
+//               contiguous and a warp's loads are whole lines.
 //   gate_norm   y = o / rms(o over the head's N values) * gain * silu(g).
 #include "common.cuh"
 
@@ -80,31 +87,38 @@ wkv_scan_kernel(float* __restrict__ o, int64_t o_stride, const float* __restrict
     if (t0 >= t1) return;
     const bool on = j < N;
     const int64_t col = (int64_t)head * N + j;
-    float* S_g = state + (int64_t)state_slots[s] * state_stride + (int64_t)head * N * N;
+    float* S_g = state + (int64_t)state_slots[s] * state_stride + (int64_t)head * N * N + (int64_t)j * N;
     float S[NMAX];
 #pragma unroll
-    for (int i = 0; i < NMAX; i++) S[i] = (on && i < N) ? S_g[(int64_t)i * N + j] : 0.f;
+    for (int i = 0; i < NMAX; i++) S[i] = (on && i < N) ? S_g[i] : 0.f;
     const float w0j = on ? w0[col] : 0.f, uj = on ? u[col] : 0.f;
 
-    auto stage = [&](int t, int buf) {
+    // a row's r, k, z, v are loaded into registers while the row before it is summed, and
+    // put into the other buffer after those sums: no load's latency stands between two rows
+    float nr = 0.f, nk = 0.f, nz = 0.f, nv = 0.f;
+    auto fetch = [&](int t) {
         if (on) {
-            const float kk = k[(int64_t)t * k_stride + col];
-            sh[buf][0][j] = r[(int64_t)t * r_stride + col];
-            sh[buf][1][j] = kk;
-            sh[buf][2][j] = expf(-expf(z[(int64_t)t * z_stride + col] + w0j));
-            sh[buf][3][j] = uj * kk;
+            nr = r[(int64_t)t * r_stride + col];
+            nk = k[(int64_t)t * k_stride + col];
+            nz = z[(int64_t)t * z_stride + col];
+            nv = v[(int64_t)t * v_stride + col];
         }
     };
-    stage(t0, 0);
-    float vj = on ? v[(int64_t)t0 * v_stride + col] : 0.f;
+    auto put = [&](int buf) {
+        if (on) {
+            sh[buf][0][j] = nr;
+            sh[buf][1][j] = nk;
+            sh[buf][2][j] = expf(-expf(nz + w0j));
+            sh[buf][3][j] = uj * nk;
+        }
+    };
+    fetch(t0);
+    put(0);
+    float vj = nv;
+    if (t0 + 1 < t1) fetch(t0 + 1);
     __syncthreads();
     for (int t = t0; t < t1; t++) {
         const int buf = (t - t0) & 1;
-        float v_next = 0.f;
-        if (t + 1 < t1) {
-            stage(t + 1, buf ^ 1);
-            v_next = on ? v[(int64_t)(t + 1) * v_stride + col] : 0.f;
-        }
         float acc = 0.f;
 #pragma unroll
         for (int i = 0; i < NMAX; i++) {
@@ -115,14 +129,114 @@ wkv_scan_kernel(float* __restrict__ o, int64_t o_stride, const float* __restrict
             }
         }
         if (on) o[(int64_t)t * o_stride + col] = acc;
-        vj = v_next;
+        if (t + 1 < t1) {
+            put(buf ^ 1);
+            vj = nv;
+            if (t + 2 < t1) fetch(t + 2);
+        }
         __syncthreads();
     }
     if (on) {
 #pragma unroll
         for (int i = 0; i < NMAX; i++)
-            if (i < N) S_g[(int64_t)i * N + j] = S[i];
+            if (i < N) S_g[i] = S[i];
     }
+}
+
+// Heads of N = 4 * IG channels, IG a power of two up to 32.  blockDim = JB * IG: JB value
+// channels j0 .. j0 + JB - 1 of one head; thread tid has g = tid % IG and j = j0 + tid / IG.
+// Rows are staged TS at a time: a batch's r, k, z, v are loaded into registers one whole
+// batch of sums before they are needed, turned into (r, k, w, u * k) and put into the
+// other shared-memory buffer after the sums of the batch in between, so that no load's
+// latency stands between two rows.
+template <int IG, int TS>
+__global__ void __launch_bounds__(256)
+wkv_scan_split_kernel(float* __restrict__ o, int64_t o_stride, const float* __restrict__ r, int64_t r_stride,
+                      const float* __restrict__ k, int64_t k_stride, const float* __restrict__ v, int64_t v_stride,
+                      const float* __restrict__ z, int64_t z_stride, const float* __restrict__ w0,
+                      const float* __restrict__ u, float* __restrict__ state, int64_t state_stride,
+                      const int* __restrict__ q_start, const int* __restrict__ state_slots) {
+    constexpr int N = 4 * IG;
+    constexpr int JB = N < 256 / IG ? N : 256 / IG;
+    constexpr int NTHR = JB * IG;
+    constexpr int ITEMS = (TS * N + NTHR - 1) / NTHR;       // (row, key channel) pairs a thread stages
+    constexpr int VITEMS = (TS * JB + NTHR - 1) / NTHR;
+    __shared__ float4 sh[2][TS][N];                         // (r, k, w, u * k) of key channel i at [(i % 4) * IG + i / 4]:
+                                                            // the lanes of a value channel read neighbouring entries
+    __shared__ float shv[2][TS][JB];
+    griddep_wait();
+    griddep_launch();
+    constexpr int jsplit = N / JB;
+    const int head = blockIdx.x / jsplit, j0 = (blockIdx.x - head * jsplit) * JB, s = blockIdx.y;
+    const int t0 = q_start[s], t1 = q_start[s + 1];
+    if (t0 >= t1) return;
+    const int tid = threadIdx.x, g = tid % IG, jl = tid / IG;
+    const int64_t base = (int64_t)head * N;
+    float4* S_g = reinterpret_cast<float4*>(state + (int64_t)state_slots[s] * state_stride + (base + j0 + jl) * N) + g;
+    const float4 S4 = *S_g;
+    float S[4] = {S4.x, S4.y, S4.z, S4.w};
+
+    float rr[ITEMS], rk[ITEMS], rz[ITEMS], rv[VITEMS];
+    auto fetch = [&](int tb) {
+#pragma unroll
+        for (int e = 0; e < ITEMS; e++) {
+            const int item = tid + e * NTHR, tt = item / N, i = item - tt * N, t = tb + tt;
+            if (item < TS * N && t < t1) {
+                rr[e] = r[(int64_t)t * r_stride + base + i];
+                rk[e] = k[(int64_t)t * k_stride + base + i];
+                rz[e] = z[(int64_t)t * z_stride + base + i];
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < VITEMS; e++) {
+            const int item = tid + e * NTHR, tt = item / JB, jj = item - tt * JB, t = tb + tt;
+            if (item < TS * JB && t < t1) rv[e] = v[(int64_t)t * v_stride + base + j0 + jj];
+        }
+    };
+    auto put = [&](int tb, int buf) {
+#pragma unroll
+        for (int e = 0; e < ITEMS; e++) {
+            const int item = tid + e * NTHR, tt = item / N, i = item - tt * N, t = tb + tt;
+            if (item < TS * N && t < t1)
+                sh[buf][tt][(i & 3) * IG + (i >> 2)] =
+                    make_float4(rr[e], rk[e], expf(-expf(rz[e] + w0[base + i])), u[base + i] * rk[e]);
+        }
+#pragma unroll
+        for (int e = 0; e < VITEMS; e++) {
+            const int item = tid + e * NTHR, tt = item / JB, jj = item - tt * JB, t = tb + tt;
+            if (item < TS * JB && t < t1) shv[buf][tt][jj] = rv[e];
+        }
+    };
+    fetch(t0);
+    put(t0, 0);
+    if (t0 + TS < t1) fetch(t0 + TS);
+    __syncthreads();
+    for (int tb = t0; tb < t1; tb += TS) {
+        const int buf = ((tb - t0) / TS) & 1;
+#pragma unroll 4
+        for (int tt = 0; tt < TS; tt++) {
+            const int t = tb + tt;
+            if (t >= t1) break;
+            const float vj = shv[buf][tt][jl];
+            float acc = 0.f;
+#pragma unroll
+            for (int ii = 0; ii < 4; ii++) {
+                const float4 c = sh[buf][tt][ii * IG + g];  // r, k, w, u * k of key channel 4g + ii
+                const float a = c.y * vj;
+                acc = fmaf(c.x, fmaf(c.w, vj, S[ii]), acc);
+                S[ii] = fmaf(c.z, S[ii], a);
+            }
+#pragma unroll
+            for (int off = IG / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+            if (g == 0) o[(int64_t)t * o_stride + base + j0 + jl] = acc;
+        }
+        if (tb + TS < t1) {
+            put(tb + TS, buf ^ 1);                          // fetched while the batch before this one ran
+            if (tb + 2 * TS < t1) fetch(tb + 2 * TS);
+        }
+        __syncthreads();
+    }
+    *S_g = make_float4(S[0], S[1], S[2], S[3]);
 }
 
 // ---- output: unit norm per head, gain, gate ---------------------------------------------
@@ -175,7 +289,7 @@ extern "C" int kllm_wkv_shift_mix(void* out, const void* h, const float* mu, flo
 }
 
 // o, r, k, v, z float32 with `heads * N` dense columns and their own row strides; w0, u float32
-// [heads * N]; the state of request s is state[state_slots[s] * state_stride ..], [heads][N][N].
+// [heads * N]; the state of request s is state[state_slots[s] * state_stride ..], [heads][N values][N keys].
 extern "C" int kllm_wkv_scan(float* o, int64_t o_stride, const float* r, int64_t r_stride, const float* k,
                              int64_t k_stride, const float* v, int64_t v_stride, const float* z, int64_t z_stride,
                              const float* w0, const float* u, float* state, int64_t state_stride, const int* q_start,
@@ -184,6 +298,18 @@ extern "C" int kllm_wkv_scan(float* o, int64_t o_stride, const float* r, int64_t
     if (heads <= 0 || N <= 0 || N > 128) KLLM_FAIL("wkv scan: %d heads of size %d (a head holds up to 128 channels)", heads, N);
     if (n_requests > 65535) KLLM_FAIL("wkv scan: %d requests in one launch", n_requests);
     cudaStream_t s = (cudaStream_t)stream;
+#define KLLM_WKV_SPLIT(IG, TS_)                                                                                        \
+    if (N == 4 * IG) {                                                                                                 \
+        constexpr int JB = 4 * IG < 256 / IG ? 4 * IG : 256 / IG;                                                      \
+        kllm_launch((wkv_scan_split_kernel<IG, TS_>), dim3(heads * (N / JB), n_requests), dim3(JB * IG), 0, s, o, o_stride, \
+                    r, r_stride, k, k_stride, v, v_stride, z, z_stride, w0, u, state, state_stride, q_start,           \
+                    state_slots);                                                                                      \
+        KLLM_LAUNCH_STATUS();                                                                                          \
+    }
+    if (state_stride % 4 == 0 && ((uintptr_t)state & 15) == 0) {
+        KLLM_WKV_SPLIT(4, 16) KLLM_WKV_SPLIT(8, 16) KLLM_WKV_SPLIT(16, 16) KLLM_WKV_SPLIT(32, 8)
+    }
+#undef KLLM_WKV_SPLIT
 #define KLLM_WKV(NMAX)                                                                                                  \
     kllm_launch((wkv_scan_kernel<NMAX>), dim3(heads, n_requests), dim3(NMAX), 0, s, o, o_stride, r, r_stride, k, k_stride, \
                 v, v_stride, z, z_stride, w0, u, state, state_stride, q_start, state_slots, N)

@@ -351,24 +351,27 @@ def attention(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: 
     over many CTAs, the portions after them the prefill form, in which a single token
     would walk its whole context with one CTA of 128 rows, 127 of them idle.
     ``score_slopes`` (a bias on the scores that is linear in the distance, per head) is
-    taken by the CUDA-core kernel only; the tensor-core kernels have no such argument.  So are
-    values of another size than the keys (``v_head_dim``) and ``exact_weights`` (the softmax
-    weights meet the values as float32 numbers; the tensor-core kernels round them to
-    bfloat16 for their second product)."""
+    taken by the CUDA-core kernel and the ``mma.sync`` kernels, not by the tcgen05 kernels.
+    ``exact_weights``: the softmax weights, computed in float32, must not meet the values
+    rounded to one bfloat16: the ``mma.sync`` kernels then feed them to the tensor cores as
+    two bfloat16 terms (16 bits of mantissa), the CUDA-core kernel as float32.  Values of
+    another size than the keys (``v_head_dim``) are taken by the CUDA-core kernel alone."""
     group = n_heads // max(1, n_kv)
     vd = int(v_head_dim or head_dim)
-    if score_slopes is not None or vd != head_dim or exact_weights:
+    special = score_slopes is not None or exact_weights
+    tc = q.dtype == torch.bfloat16 and head_dim in TC_HEAD_DIMS and vd == head_dim and not (special and scale <= 0)
+    if (special or vd != head_dim) and not (tc and group <= 64):
         if not simt_fits(q, n_heads, n_kv, head_dim, vd):
             raise KernelError("attention: a bias on the scores, values of another size than the keys or float32 "
                               "weights need head sizes that are multiples of 4 up to 256, at most 64 heads per kv "
                               "head and rows aligned to four elements")
         return attention_simt(out, q, kcache, vcache, ctx, block_table, n_heads, n_kv, head_dim, window, scale,
                               score_slopes, vd)
-    tc = q.dtype == torch.bfloat16 and head_dim in TC_HEAD_DIMS
     if tc and ctx.all_single and group <= 16:
         return attention_decode(out, q, kcache, vcache, ctx.positions, ctx.token_req, block_table, n_heads,
                                 n_kv, head_dim, window, scale,
-                                decode_splits(ctx.n_tokens, n_kv, ctx.split_bound or ctx.max_ctx))
+                                decode_splits(ctx.n_tokens, n_kv, ctx.split_bound or ctx.max_ctx),
+                                slopes=score_slopes, split_weights=exact_weights)
     singles = 0
     if tc and group <= 16 and ctx.host_n_new:
         while singles < ctx.n_requests and ctx.host_n_new[singles] == 1:
@@ -377,18 +380,19 @@ def attention(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: 
         # token t of the first `singles` is request t: no token-to-request table needed
         attention_decode(out[:singles], q[:singles], kcache, vcache, ctx.positions[:singles], None,
                          block_table[:singles], n_heads, n_kv, head_dim, window, scale,
-                         decode_splits(singles, n_kv, ctx.max_ctx))
+                         decode_splits(singles, n_kv, ctx.max_ctx), slopes=score_slopes, split_weights=exact_weights)
     q_start, start_pos, table, n_req = ctx.q_start, ctx.start_pos, block_table, ctx.n_requests
     if 0 < singles < ctx.n_requests:
         q_start, start_pos, table, n_req = q_start[singles:], start_pos[singles:], block_table[singles:], n_req - singles
-    if tc and USE_TCGEN05 and head_dim in TCGEN05_HEAD_DIMS and group <= 128:
+    if tc and USE_TCGEN05 and head_dim in TCGEN05_HEAD_DIMS and group <= 128 and not special:
         return attention_prefill_tcgen05(out, q, kcache, vcache, q_start, start_pos, table,
                                          n_req, n_heads, n_kv, head_dim, window, scale,
                                          probabilities=tcgen05_form(head_dim, group, n_kv, ctx.n_tokens - singles,
                                                                     n_req, ctx.max_ctx))
     if tc and group <= 64:
         return attention_prefill(out, q, kcache, vcache, q_start, start_pos, table,
-                                 n_req, n_heads, n_kv, head_dim, window, scale)
+                                 n_req, n_heads, n_kv, head_dim, window, scale, slopes=score_slopes,
+                                 split_weights=exact_weights)
     if simt_fits(q, n_heads, n_kv, head_dim):
         return attention_simt(out, q, kcache, vcache, ctx, block_table, n_heads, n_kv, head_dim, window, scale)
     return attention_generic(out, q, kcache, vcache, ctx.positions, ctx.token_req, block_table, n_heads, n_kv,
@@ -405,11 +409,20 @@ def _check_attention(out, q, kcache, vcache, block_table, n_kv, head_dim):
     _i32(block_table, "block_table")
 
 
+def _slopes_arg(slopes, n_heads):
+    if slopes is not None and (slopes.dtype != torch.float32 or not slopes.is_contiguous() or slopes.numel() != n_heads):
+        raise KernelError("attention: score slopes must be a contiguous float32 tensor, one per head")
+    return _p(slopes)
+
+
 def attention_decode(out, q, kcache, vcache, positions, token_req, block_table, n_heads, n_kv, head_dim,
-                     window, scale, num_splits: int) -> None:
+                     window, scale, num_splits: int, slopes: Optional[torch.Tensor] = None,
+                     split_weights: bool = False) -> None:
     """Tensor-core decode attention: every token attends on its own, its keys cut
-    into ``num_splits`` ranges that are merged in a fixed order."""
-    _cuda(out, q, kcache, vcache, positions, token_req, block_table)
+    into ``num_splits`` ranges that are merged in a fixed order.  ``slopes`` (float32 [heads]):
+    slope[h] * (key position - query position) is added to the scaled scores; ``split_weights``:
+    the probabilities enter the second product as two bfloat16 terms instead of one."""
+    _cuda(out, q, kcache, vcache, positions, token_req, block_table, slopes)
     _check_attention(out, q, kcache, vcache, block_table, n_kv, head_dim)
     _i32(positions, "positions"); _i32(token_req, "token_req")
     n = q.shape[0]
@@ -421,7 +434,8 @@ def attention_decode(out, q, kcache, vcache, positions, token_req, block_table, 
     rc = lib.kllm_attention_decode(_p(out), _p(part_o), _p(part_ml), _p(q), ctypes.c_int64(q.stride(0)),
                                    _p(kcache), _p(vcache), _p(positions), _p(token_req), _p(block_table),
                                    block_table.shape[1], n, n_heads, n_kv, head_dim, kcache.shape[2],
-                                   int(window or 0), ctypes.c_float(scale), int(num_splits), _stream())
+                                   int(window or 0), ctypes.c_float(scale), int(num_splits), _slopes_arg(slopes, n_heads),
+                                   int(bool(split_weights)), _stream())
     _check(lib, "attention_tc", rc)
     global launches
     if num_splits > 1:
@@ -463,17 +477,20 @@ def attention_decode_fused(out, q, k_new, v_new, cos_sin, kcache, vcache, positi
 
 
 def attention_prefill(out, q, kcache, vcache, q_start, start_pos, block_table, n_requests, n_heads, n_kv,
-                      head_dim, window, scale) -> None:
+                      head_dim, window, scale, slopes: Optional[torch.Tensor] = None,
+                      split_weights: bool = False) -> None:
     """Tensor-core attention of portions: request s brings rows q_start[s]..q_start[s+1]
-    that start at cache position start_pos[s]."""
-    _cuda(out, q, kcache, vcache, q_start, start_pos, block_table)
+    that start at cache position start_pos[s].  ``slopes`` and ``split_weights`` as in
+    ``attention_decode``."""
+    _cuda(out, q, kcache, vcache, q_start, start_pos, block_table, slopes)
     _check_attention(out, q, kcache, vcache, block_table, n_kv, head_dim)
     _i32(q_start, "q_start"); _i32(start_pos, "start_pos")
     lib = load_library("attention_tc", {"KLLM_HD": head_dim})
     rc = lib.kllm_attention_prefill(_p(out), _p(q), ctypes.c_int64(q.stride(0)), _p(kcache), _p(vcache),
                                     _p(q_start), _p(start_pos), _p(block_table), block_table.shape[1],
                                     q.shape[0], int(n_requests), n_heads, n_kv, head_dim, kcache.shape[2],
-                                    int(window or 0), ctypes.c_float(scale), _stream())
+                                    int(window or 0), ctypes.c_float(scale), _slopes_arg(slopes, n_heads),
+                                    int(bool(split_weights)), _stream())
     _check(lib, "attention_tc", rc)
 
 
@@ -854,6 +871,32 @@ def gemm(x: torch.Tensor, weight: torch.Tensor, *, epilogue: str = "bf16", out: 
                                _stream())
     _check(lib, "gemm_tcgen05", rc)
     return out
+
+
+_bmm_takes_out_dtype = None
+
+
+def linear_batched(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """y[b] = x[b] @ weight[b]^T in float32 for stacked operands x [B, n, K], weight [B, N, K]
+    through the vendor GEMM library (one batched product; bfloat16 operands accumulate and
+    come out in float32, float32 operands run as true float32)."""
+    global _bmm_takes_out_dtype
+    _cuda(x, weight)
+    if torch.backends.cuda.matmul.allow_tf32:
+        raise KernelError("TF32 matmul mode is on; the float32 path must stay true 32-bit")
+    wt = weight.transpose(1, 2)
+    if x.dtype == torch.float32:
+        return torch.bmm(x, wt)
+    if _bmm_takes_out_dtype is None:
+        try:
+            y = torch.bmm(x, wt, out_dtype=torch.float32)
+            _bmm_takes_out_dtype = True
+            return y
+        except (TypeError, RuntimeError):
+            _bmm_takes_out_dtype = False
+    if _bmm_takes_out_dtype:
+        return torch.bmm(x, wt, out_dtype=torch.float32)
+    return torch.stack([torch.mm(x[i], wt[i], out_dtype=torch.float32) for i in range(x.shape[0])])
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None,

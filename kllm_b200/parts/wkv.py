@@ -15,8 +15,9 @@ heads' unit norm), ``decay_rank`` (rows of W_w1 for random weights; a file's own
 taken from its tensor), optional ``tensors`` (name -> full tensor name for mu.r .. mu.w, r,
 k, v, g, w1, w2, w0, u, norm, o; default ``<prefix>.<name>``).
 
-State (``StateNeed``): per request one float32 vector, [heads * size * size] for S followed
-by [hidden] for the last row of h that the request has seen, zero when the request opens.
+State (``StateNeed``): per request one float32 vector, [heads][value channel][key channel] for
+S followed by [hidden] for the last row of h that the request has seen (rounded up to a
+multiple of four floats), zero when the request opens.
 Decay, state, sums, unit norm and gate are float32 in both dtypes; the projections take
 inputs in the model dtype and hand their results on unrounded (float32).  Kernels:
 csrc/wkv.cu (token shift, recurrence, unit norm and gate); the projections are library
@@ -48,7 +49,7 @@ class WkvMixer:
         names = dict(p.get("tensors") or {})
         self.n = {k: names.get(k) or f"{spec.prefix}.{k}" for k in
                   [f"mu.{s}" for s in _MIX] + ["r", "k", "v", "g", "w1", "w2", "w0", "u", "norm", "o"]}
-        self.state_size = self.inner * self.size + self.hidden
+        self.state_size = -(-(self.inner * self.size + self.hidden) // 4) * 4    # whole 16-byte units per slot
 
     def tensor_specs(self):
         n, d, A = self.n, self.hidden, self.inner
@@ -62,7 +63,8 @@ class WkvMixer:
     def bind(self, tensors):
         n = self.n
         self.mu = torch.stack([tensors[n[f"mu.{s}"]] for s in _MIX]).contiguous()
-        self.w_r, self.w_k, self.w_v, self.w_g = (tensors[n[s]] for s in ("r", "k", "v", "g"))
+        # the four projections read four inputs: one batched product over the stacked matrices
+        self.w_rkvg = torch.stack([tensors[n[s]] for s in ("r", "k", "v", "g")]).contiguous()
         self.w1, self.w2 = tensors[n["w1"]], tensors[n["w2"]]
         if self.w1.shape[0] != self.w2.shape[1]:
             raise ValueError(f"wkv: the decay's two matrices disagree on its rank ({tuple(self.w1.shape)}, "
@@ -79,10 +81,7 @@ class WkvMixer:
         f32 = torch.float32
         state = cache.state
         mix = kernels.wkv_shift_mix(xn, self.mu, state, self.inner * self.size, ctx)
-        r = kernels.linear(mix[0], self.w_r, out_dtype=f32)
-        k = kernels.linear(mix[1], self.w_k, out_dtype=f32)
-        v = kernels.linear(mix[2], self.w_v, out_dtype=f32)
-        g = kernels.linear(mix[3], self.w_g, out_dtype=f32)
+        r, k, v, g = kernels.linear_batched(mix[:4], self.w_rkvg)
         low = kernels.unary(kernels.linear(mix[4], self.w1, out_dtype=f32), "tanh", self.dtype)
         z = kernels.linear(low, self.w2, out_dtype=f32)
         o = kernels.wkv_scan(r, k, v, z, self.w0, self.u, state, ctx, self.heads, self.size)

@@ -261,7 +261,7 @@ def test_wkv_scan_carries_its_state(size, heads):
     r, k, v = (rng.standard_normal((sum(lens), A)) for _ in range(3))
     z = rng.uniform(-5, 1, (sum(lens), A))
     w0, u = rng.uniform(-1, 0.5, A), rng.standard_normal(A)
-    state = torch.full((3, A * size + 7), 0.0, device="cuda")
+    state = torch.full((3, A * size + 8), 0.0, device="cuda")
     slots = [2, 0]
     outs = []
     cuts = [(0, 14), (0, 4)], [(14, 23), (4, 9)]
@@ -278,7 +278,7 @@ def test_wkv_scan_carries_its_state(size, heads):
         sl = slice(offs[s], offs[s] + lens[s])
         want, S = P.wkv_scan(r[sl], k[sl], v[sl], np.exp(-np.exp(z[sl] + w0)), u, heads, size)
         assert np.abs(got[sl] - want).max() <= 2e-5 * np.abs(want).max()
-        S_got = state[slots[s], :A * size].cpu().numpy().reshape(heads, size, size)
+        S_got = state[slots[s], :A * size].cpu().numpy().reshape(heads, size, size).transpose(0, 2, 1)   # [h][j][i] in the slot
         assert np.abs(S_got - S).max() <= 2e-5 * np.abs(S).max()
     assert float(state[1].abs().max()) == 0.0 and float(state[:, A * size:].abs().max()) == 0.0
 
@@ -413,12 +413,15 @@ def test_qk_norm_temperature_and_cache_write(dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("E,top,on", [(8, 1, "input"), (5, 3, "input"), (4, 4, "output"), (40, 2, "input")])
-def test_routed_experts(dtype, E, top, on):
+@pytest.mark.parametrize("E,top,on,d,f", [(8, 1, "input", 36, 28), (5, 3, "input", 40, 24), (4, 4, "output", 72, 100),
+                                          (40, 2, "input", 64, 30), (3, 2, "input", 200, 136)])
+def test_routed_experts(dtype, E, top, on, d, f):
+    """Widths that are and are not multiples of 8 (the tensor-core tiles want 16-byte rows; the
+    others run on the CUDA cores), feed-forward sizes that do not fill a tile."""
     import torch
     from kllm_b200 import kernels
     rng = np.random.default_rng(E)
-    n, d, f = 77, 36, 28
+    n = 77
     h = P.round_bf16(rng.standard_normal((n, d)))
     w = {"router": rng.standard_normal((E, d))}
     for e in range(E):
