@@ -150,7 +150,7 @@ wkv_scan_kernel(float* __restrict__ o, int64_t o_stride, const float* __restrict
 // other shared-memory buffer after the sums of the batch in between, so that no load's
 // latency stands between two rows.
 template <int IG, int TS>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 wkv_scan_split_kernel(float* __restrict__ o, int64_t o_stride, const float* __restrict__ r, int64_t r_stride,
                       const float* __restrict__ k, int64_t k_stride, const float* __restrict__ v, int64_t v_stride,
                       const float* __restrict__ z, int64_t z_stride, const float* __restrict__ w0,
@@ -213,10 +213,7 @@ wkv_scan_split_kernel(float* __restrict__ o, int64_t o_stride, const float* __re
     __syncthreads();
     for (int tb = t0; tb < t1; tb += TS) {
         const int buf = ((tb - t0) / TS) & 1;
-#pragma unroll 4
-        for (int tt = 0; tt < TS; tt++) {
-            const int t = tb + tt;
-            if (t >= t1) break;
+        auto row = [&](int tt) {
             const float vj = shv[buf][tt][jl];
             float acc = 0.f;
 #pragma unroll
@@ -226,9 +223,33 @@ wkv_scan_split_kernel(float* __restrict__ o, int64_t o_stride, const float* __re
                 acc = fmaf(c.x, fmaf(c.w, vj, S[ii]), acc);
                 S[ii] = fmaf(c.z, S[ii], a);
             }
+            return acc;
+        };
+        if (tb + TS <= t1) {
+            // a whole batch, four rows at a time: the rows' sums one after the other (the state
+            // runs through them), then the lanes' parts of all four added together, so that the
+            // shuffles of one row do not wait for those of the row before
 #pragma unroll
-            for (int off = IG / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-            if (g == 0) o[(int64_t)t * o_stride + base + j0 + jl] = acc;
+            for (int tt = 0; tt < TS; tt += 4) {
+                float acc[4];
+#pragma unroll
+                for (int q = 0; q < 4; q++) acc[q] = row(tt + q);
+#pragma unroll
+                for (int off = IG / 2; off > 0; off >>= 1)
+#pragma unroll
+                    for (int q = 0; q < 4; q++) acc[q] += __shfl_xor_sync(0xffffffffu, acc[q], off);
+                if (g == 0) {
+#pragma unroll
+                    for (int q = 0; q < 4; q++) o[(int64_t)(tb + tt + q) * o_stride + base + j0 + jl] = acc[q];
+                }
+            }
+        } else {
+            for (int tt = 0; tb + tt < t1; tt++) {
+                float acc = row(tt);
+#pragma unroll
+                for (int off = IG / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+                if (g == 0) o[(int64_t)(tb + tt) * o_stride + base + j0 + jl] = acc;
+            }
         }
         if (tb + TS < t1) {
             put(tb + TS, buf ^ 1);                          // fetched while the batch before this one ran
