@@ -19,11 +19,11 @@
 //               before in the same request, or the request's last row of the step before
 //               (kept in its state slot, zeros at the start); the slot is updated.
 //   scan        the recurrence above over the rows of every request.  Heads of 16, 32, 64 or
-//               128 channels: a CTA per (head, slice of value channels, request); thread
-//               (j, g) keeps S[4g .. 4g+3][j] in registers, the N/4 threads of a value
-//               channel are neighbouring lanes and add their parts of o_j by shuffles in a
-//               fixed tree; r, k, the decay and u*k of four rows at a time are staged in
-//               shared memory (two buffers, one barrier per four rows).  Other head sizes
+//               128 channels: a CTA per (head, slice of value channels, request); a thread
+//               keeps S[4g .. 4g+3][j] of up to four value channels j in registers, the N/4
+//               threads of a value channel are neighbouring lanes and add their parts of o_j
+//               by shuffles in a fixed tree; r, k, the decay and u*k of eight rows at a time
+//               are staged in shared memory (two buffers, one barrier per eight rows).  Other head sizes
 //               up to 128: one CTA per (head, request), thread j owning all of S[.][j].
 //               In the slot the state lies as [heads][j][i], so a thread's part is
 //               contiguous and a warp's loads are whole lines.
@@ -143,22 +143,34 @@ wkv_scan_kernel(float* __restrict__ o, int64_t o_stride, const float* __restrict
     }
 }
 
-// Heads of N = 4 * IG channels, IG a power of two up to 32.  blockDim = JB * IG: JB value
-// channels j0 .. j0 + JB - 1 of one head; thread tid has g = tid % IG and j = j0 + tid / IG.
-// Rows are staged TS at a time: a batch's r, k, z, v are loaded into registers one whole
-// batch of sums before they are needed, turned into (r, k, w, u * k) and put into the
-// other shared-memory buffer after the sums of the batch in between, so that no load's
-// latency stands between two rows.
-template <int IG, int TS>
-__global__ void __launch_bounds__(256, 2)
+// Heads of N = 4 * IG channels, IG a power of two up to 32.  A CTA has JB value channels j0 ..
+// j0 + JB - 1 of one head and (JB / JT) * IG threads; thread tid has g = tid % IG (key channels
+// 4g .. 4g + 3) and JT value channels j0 + tid / IG + q * (JB / JT): what it reads of a row's
+// (r, k, w, u k) from shared memory serves JT value channels, and shared-memory bandwidth is what
+// bounds this kernel.  Rows are staged TS at a time: a batch's r, k, z, v are loaded into
+// registers one whole batch of sums before they are needed, turned into (r, k, w, u * k) and
+// put into the other shared-memory buffer after the sums of the batch in between, so that no
+// load's latency stands between two rows.
+// JT = 1 (many threads, short chains per row) is the faster form while the CTAs are few enough
+// to be resident together, JT = 4 once they queue; a value channel's additions are the same in
+// both, so the choice changes no bit of the result.
+template <int IG, int JT_> struct WkvSplit {
+    static constexpr int N = 4 * IG;
+    static constexpr int JB = N < 256 / IG ? N : 256 / IG;
+    static constexpr int JT = JT_;
+    static constexpr int NTHR = JB / JT * IG;
+    static constexpr int TS = (JT == 1 && N <= 64) ? 16 : 8;
+};
+
+template <int IG, int JT_>
+__global__ void __launch_bounds__(WkvSplit<IG, JT_>::NTHR, JT_ == 1 ? 2 : 1)
 wkv_scan_split_kernel(float* __restrict__ o, int64_t o_stride, const float* __restrict__ r, int64_t r_stride,
                       const float* __restrict__ k, int64_t k_stride, const float* __restrict__ v, int64_t v_stride,
                       const float* __restrict__ z, int64_t z_stride, const float* __restrict__ w0,
                       const float* __restrict__ u, float* __restrict__ state, int64_t state_stride,
                       const int* __restrict__ q_start, const int* __restrict__ state_slots) {
-    constexpr int N = 4 * IG;
-    constexpr int JB = N < 256 / IG ? N : 256 / IG;
-    constexpr int NTHR = JB * IG;
+    using C = WkvSplit<IG, JT_>;
+    constexpr int N = C::N, JB = C::JB, JT = C::JT, NTHR = C::NTHR, TS = C::TS, JQ = JB / JT;
     constexpr int ITEMS = (TS * N + NTHR - 1) / NTHR;       // (row, key channel) pairs a thread stages
     constexpr int VITEMS = (TS * JB + NTHR - 1) / NTHR;
     __shared__ float4 sh[2][TS][N];                         // (r, k, w, u * k) of key channel i at [(i % 4) * IG + i / 4]:
@@ -170,11 +182,15 @@ wkv_scan_split_kernel(float* __restrict__ o, int64_t o_stride, const float* __re
     const int head = blockIdx.x / jsplit, j0 = (blockIdx.x - head * jsplit) * JB, s = blockIdx.y;
     const int t0 = q_start[s], t1 = q_start[s + 1];
     if (t0 >= t1) return;
-    const int tid = threadIdx.x, g = tid % IG, jl = tid / IG;
+    const int tid = threadIdx.x, g = tid % IG, jq = tid / IG;
     const int64_t base = (int64_t)head * N;
-    float4* S_g = reinterpret_cast<float4*>(state + (int64_t)state_slots[s] * state_stride + (base + j0 + jl) * N) + g;
-    const float4 S4 = *S_g;
-    float S[4] = {S4.x, S4.y, S4.z, S4.w};
+    float* S_base = state + (int64_t)state_slots[s] * state_stride + (base + j0 + jq) * N + 4 * g;
+    float S[JT][4];
+#pragma unroll
+    for (int q = 0; q < JT; q++) {
+        const float4 S4 = *reinterpret_cast<const float4*>(S_base + (int64_t)q * JQ * N);
+        S[q][0] = S4.x; S[q][1] = S4.y; S[q][2] = S4.z; S[q][3] = S4.w;
+    }
 
     float rr[ITEMS], rk[ITEMS], rz[ITEMS], rv[VITEMS];
     auto fetch = [&](int tb) {
@@ -213,43 +229,52 @@ wkv_scan_split_kernel(float* __restrict__ o, int64_t o_stride, const float* __re
     __syncthreads();
     for (int tb = t0; tb < t1; tb += TS) {
         const int buf = ((tb - t0) / TS) & 1;
-        auto row = [&](int tt) {
-            const float vj = shv[buf][tt][jl];
-            float acc = 0.f;
+        // one row: the thread's parts of o for its JT value channels; the order of a value
+        // channel's additions (key channels 4g .. 4g + 3, then the lanes' tree) is fixed
+        auto sums = [&](int tt, float (&acc)[JT]) {
+            float vj[JT];
+#pragma unroll
+            for (int q = 0; q < JT; q++) {
+                vj[q] = shv[buf][tt][jq + q * JQ];
+                acc[q] = 0.f;
+            }
 #pragma unroll
             for (int ii = 0; ii < 4; ii++) {
                 const float4 c = sh[buf][tt][ii * IG + g];  // r, k, w, u * k of key channel 4g + ii
-                const float a = c.y * vj;
-                acc = fmaf(c.x, fmaf(c.w, vj, S[ii]), acc);
-                S[ii] = fmaf(c.z, S[ii], a);
-            }
-            return acc;
-        };
-        if (tb + TS <= t1) {
-            // a whole batch, four rows at a time: the rows' sums one after the other (the state
-            // runs through them), then the lanes' parts of all four added together, so that the
-            // shuffles of one row do not wait for those of the row before
 #pragma unroll
-            for (int tt = 0; tt < TS; tt += 4) {
-                float acc[4];
-#pragma unroll
-                for (int q = 0; q < 4; q++) acc[q] = row(tt + q);
-#pragma unroll
-                for (int off = IG / 2; off > 0; off >>= 1)
-#pragma unroll
-                    for (int q = 0; q < 4; q++) acc[q] += __shfl_xor_sync(0xffffffffu, acc[q], off);
-                if (g == 0) {
-#pragma unroll
-                    for (int q = 0; q < 4; q++) o[(int64_t)(tb + tt + q) * o_stride + base + j0 + jl] = acc[q];
+                for (int q = 0; q < JT; q++) {
+                    const float a = c.y * vj[q];
+                    acc[q] = fmaf(c.x, fmaf(c.w, vj[q], S[q][ii]), acc[q]);
+                    S[q][ii] = fmaf(c.z, S[q][ii], a);
                 }
             }
-        } else {
-            for (int tt = 0; tb + tt < t1; tt++) {
-                float acc = row(tt);
+        };
+        constexpr int RG = JT >= 4 ? 1 : 4 / JT;            // rows whose lane sums are formed together
+        auto rows = [&](int tt, int n_rows) {
+            float acc[RG][JT];
 #pragma unroll
-                for (int off = IG / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-                if (g == 0) o[(int64_t)(tb + tt) * o_stride + base + j0 + jl] = acc;
+            for (int p = 0; p < RG; p++)
+                if (p < n_rows) sums(tt + p, acc[p]);
+#pragma unroll
+            for (int off = IG / 2; off > 0; off >>= 1)
+#pragma unroll
+                for (int p = 0; p < RG; p++)
+#pragma unroll
+                    for (int q = 0; q < JT; q++) acc[p][q] += __shfl_xor_sync(0xffffffffu, acc[p][q], off);
+            if (g == 0) {
+#pragma unroll
+                for (int p = 0; p < RG; p++)
+#pragma unroll
+                    for (int q = 0; q < JT; q++)
+                        if (p < n_rows) o[(int64_t)(tb + tt + p) * o_stride + base + j0 + jq + q * JQ] = acc[p][q];
             }
+        };
+        if (tb + TS <= t1) {
+            // a whole batch: no branch between the rows, so that their loads and shuffles overlap
+#pragma unroll
+            for (int tt = 0; tt < TS; tt += RG) rows(tt, RG);
+        } else {
+            for (int tt = 0; tb + tt < t1; tt += RG) rows(tt, min(RG, t1 - tb - tt));
         }
         if (tb + TS < t1) {
             put(tb + TS, buf ^ 1);                          // fetched while the batch before this one ran
@@ -257,7 +282,9 @@ wkv_scan_split_kernel(float* __restrict__ o, int64_t o_stride, const float* __re
         }
         __syncthreads();
     }
-    *S_g = make_float4(S[0], S[1], S[2], S[3]);
+#pragma unroll
+    for (int q = 0; q < JT; q++)
+        *reinterpret_cast<float4*>(S_base + (int64_t)q * JQ * N) = make_float4(S[q][0], S[q][1], S[q][2], S[q][3]);
 }
 
 // ---- output: unit norm per head, gain, gate ---------------------------------------------
@@ -319,17 +346,24 @@ extern "C" int kllm_wkv_scan(float* o, int64_t o_stride, const float* r, int64_t
     if (heads <= 0 || N <= 0 || N > 128) KLLM_FAIL("wkv scan: %d heads of size %d (a head holds up to 128 channels)", heads, N);
     if (n_requests > 65535) KLLM_FAIL("wkv scan: %d requests in one launch", n_requests);
     cudaStream_t s = (cudaStream_t)stream;
-#define KLLM_WKV_SPLIT(IG, TS_)                                                                                        \
-    if (N == 4 * IG) {                                                                                                 \
-        constexpr int JB = 4 * IG < 256 / IG ? 4 * IG : 256 / IG;                                                      \
-        kllm_launch((wkv_scan_split_kernel<IG, TS_>), dim3(heads * (N / JB), n_requests), dim3(JB * IG), 0, s, o, o_stride, \
-                    r, r_stride, k, k_stride, v, v_stride, z, z_stride, w0, u, state, state_stride, q_start,           \
+#define KLLM_WKV_SPLIT_JT(IG, JT)                                                                                      \
+    {                                                                                                                  \
+        using C = WkvSplit<IG, JT>;                                                                                    \
+        kllm_launch((wkv_scan_split_kernel<IG, JT>), dim3(heads * (C::N / C::JB), n_requests), dim3(C::NTHR), 0, s, o, \
+                    o_stride, r, r_stride, k, k_stride, v, v_stride, z, z_stride, w0, u, state, state_stride, q_start, \
                     state_slots);                                                                                      \
         KLLM_LAUNCH_STATUS();                                                                                          \
     }
-    if (state_stride % 4 == 0 && ((uintptr_t)state & 15) == 0) {
-        KLLM_WKV_SPLIT(4, 16) KLLM_WKV_SPLIT(8, 16) KLLM_WKV_SPLIT(16, 16) KLLM_WKV_SPLIT(32, 8)
+#define KLLM_WKV_SPLIT(IG)                                                                                             \
+    if (N == 4 * IG) {                                                                                                 \
+        constexpr int JB = WkvSplit<IG, 1>::JB;                                                                        \
+        if (JB * IG < 256 || (int64_t)heads * (4 * IG / JB) * n_requests <= 2 * 148) KLLM_WKV_SPLIT_JT(IG, 1)           \
+        KLLM_WKV_SPLIT_JT(IG, (JB * IG >= 256 ? 4 : 1))                                                                \
     }
+    if (state_stride % 4 == 0 && ((uintptr_t)state & 15) == 0) {
+        KLLM_WKV_SPLIT(4) KLLM_WKV_SPLIT(8) KLLM_WKV_SPLIT(16) KLLM_WKV_SPLIT(32)
+    }
+#undef KLLM_WKV_SPLIT_JT
 #undef KLLM_WKV_SPLIT
 #define KLLM_WKV(NMAX)                                                                                                  \
     kllm_launch((wkv_scan_kernel<NMAX>), dim3(heads, n_requests), dim3(NMAX), 0, s, o, o_stride, r, r_stride, k, k_stride, \

@@ -900,14 +900,22 @@ def linear_batched(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None,
-           out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+           out_dtype: Optional[torch.dtype] = None, small_ok: bool = False) -> torch.Tensor:
     """y = x @ weight^T through the vendor GEMM library (cuBLAS, via torch.mm), as
     the reference does for every projection (backend/model.cu:496-503).
 
     float32 operands run as true float32 (the reduced-precision TF32 mode stays
-    off); bfloat16 operands accumulate in float32.
+    off); bfloat16 operands accumulate in float32.  ``small_ok`` with a float32 result: a step
+    of a few rows (``skinny_fits``) takes this repository's weight-streaming product instead,
+    which reads the matrix once at the speed of HBM; which of the two runs depends on the row
+    count alone.
     """
     _cuda(x, weight)
+    if (small_ok and out is None and out_dtype == torch.float32 and x.dtype == weight.dtype and x.dim() == 2
+            and x.stride(1) == 1 and weight.stride(1) == 1 and skinny_fits(x.shape[0], x.shape[1], x.dtype)
+            and weight.stride(0) % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+            and weight.data_ptr() % 16 == 0):
+        return skinny_gemm(weight, x=x, epilogue="f32")
     if torch.backends.cuda.matmul.allow_tf32:
         raise KernelError("TF32 matmul mode is on; the float32 path must stay true 32-bit")
     if out_dtype is not None and out_dtype != x.dtype:

@@ -188,8 +188,8 @@ class PagedAttention:
         # a layer that reads another layer's cache projects its queries only
         w = self.w_qkv if cache.writes else self.w_qkv[:self.q_dim]
         if self._prepares:
-            attn = self._attend_prepared(kernels.linear(xn, w, out_dtype=torch.float32), ctx, cache)
-            return kernels.linear(attn, self.w_o, out_dtype=torch.float32)
+            attn = self._attend_prepared(kernels.linear(xn, w, out_dtype=torch.float32, small_ok=True), ctx, cache)
+            return kernels.linear(attn, self.w_o, out_dtype=torch.float32, small_ok=True)
         q, k, v = self._split(kernels.linear(xn, w), cache.writes)
         attn = self._attend(q, k, v, ctx, cache)
         # float32 out: the result goes into the residual stream unrounded

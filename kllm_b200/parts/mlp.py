@@ -120,8 +120,9 @@ class PlainMLP:
         self.w_up, self.w_down = tensors[self.up_name], tensors[self.down_name]
 
     def forward(self, xn, ctx):
-        act = kernels.unary(kernels.linear(xn, self.w_up, out_dtype=torch.float32), self.activation, self.dtype)
-        return kernels.linear(act, self.w_down, out_dtype=torch.float32)
+        act = kernels.unary(kernels.linear(xn, self.w_up, out_dtype=torch.float32, small_ok=True), self.activation,
+                            self.dtype)
+        return kernels.linear(act, self.w_down, out_dtype=torch.float32, small_ok=True)
 
 
 register_part("feed_forward", "gated_mlp", GatedMLP)

@@ -81,12 +81,16 @@ class WkvMixer:
         f32 = torch.float32
         state = cache.state
         mix = kernels.wkv_shift_mix(xn, self.mu, state, self.inner * self.size, ctx)
-        r, k, v, g = kernels.linear_batched(mix[:4], self.w_rkvg)
-        low = kernels.unary(kernels.linear(mix[4], self.w1, out_dtype=f32), "tanh", self.dtype)
-        z = kernels.linear(low, self.w2, out_dtype=f32)
+        if kernels.skinny_fits(xn.shape[0], self.hidden, self.dtype):
+            # a few rows: four weight-streaming products instead of one batched library product
+            r, k, v, g = (kernels.linear(mix[i], self.w_rkvg[i], out_dtype=f32, small_ok=True) for i in range(4))
+        else:
+            r, k, v, g = kernels.linear_batched(mix[:4], self.w_rkvg)
+        low = kernels.unary(kernels.linear(mix[4], self.w1, out_dtype=f32, small_ok=True), "tanh", self.dtype)
+        z = kernels.linear(low, self.w2, out_dtype=f32, small_ok=True)
         o = kernels.wkv_scan(r, k, v, z, self.w0, self.u, state, ctx, self.heads, self.size)
         y = kernels.wkv_gate_norm(o, g, self.gain, self.eps, self.heads, self.size, self.dtype)
-        return kernels.linear(y, self.w_o, out_dtype=f32)
+        return kernels.linear(y, self.w_o, out_dtype=f32, small_ok=True)
 
 
 register_part("mixer", "wkv", WkvMixer)
