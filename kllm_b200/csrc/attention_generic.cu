@@ -1,6 +1,7 @@
 // Causal grouped-query attention over the paged cache, generic form: any head
-// size up to 256 (even), any number of heads and kv heads, any query length, an
-// optional window, float32 arithmetic throughout.  It is the whole attention of
+// size up to 256, values of their own size, any number of heads and kv heads, any query
+// length, an optional window, an optional bias on the scores that is linear in the distance
+// (slope[head] * (key position - query position)), float32 arithmetic throughout.  It is the whole attention of
 // the float32 path and the fallback of the bfloat16 path for head sizes that the
 // tensor-core kernels do not take.
 //
@@ -28,7 +29,8 @@ attn_generic_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q_stri
                     const T* __restrict__ kcache, const T* __restrict__ vcache,
                     const int* __restrict__ positions, const int* __restrict__ token_req,
                     const int* __restrict__ block_table, int max_blocks, int n_tokens,
-                    int n_heads, int n_kv, int hd, int page_size, int window, float scale) {
+                    int n_heads, int n_kv, int hd, int vd, int page_size, int window, float scale,
+                    const float* __restrict__ slopes) {
     __shared__ float qs[kWarps][kMaxHd];
     griddep_wait();
     griddep_launch();
@@ -46,8 +48,7 @@ attn_generic_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q_stri
     for (int i = lane; i < hd; i += 32) qs[warp][i] = to_f32(qr[i]);
     __syncwarp();
 
-    const int64_t head_off = (int64_t)g * page_size * hd;
-    const int64_t page_elems = (int64_t)n_kv * page_size * hd;
+    const float slope = slopes ? slopes[h] : 0.f;
     float acc[kMaxHd / 32];
 #pragma unroll
     for (int i = 0; i < kMaxHd / 32; i++) acc[i] = 0.f;
@@ -59,11 +60,11 @@ attn_generic_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q_stri
         int64_t row = 0;
         if (key < len) {
             const int page = table[key / page_size];
-            row = (int64_t)page * page_elems + head_off + (int64_t)(key % page_size) * hd;
-            const T* kr = kcache + row;
+            row = ((int64_t)page * n_kv + g) * page_size + (key % page_size);      // the key's row in both caches
+            const T* kr = kcache + row * hd;
             float dot = 0.f;
             for (int d = 0; d < hd; d++) dot += qs[warp][d] * to_f32(kr[d]);
-            sc = dot * scale;
+            sc = dot * scale + slope * (float)(key - p);
         }
         const float m_new = fmaxf(m, warp_max(sc));
         const float corr = expf(m - m_new);  // 0 on the first chunk (m = -inf)
@@ -76,35 +77,37 @@ attn_generic_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q_stri
         for (int j = 0; j < cnt; j++) {
             const float pj = __shfl_sync(0xffffffffu, pr, j);
             const int64_t rj = __shfl_sync(0xffffffffu, row, j);
-            const T* vr = vcache + rj;
+            const T* vr = vcache + rj * vd;
 #pragma unroll
             for (int i = 0; i < kMaxHd / 32; i++) {
                 const int d = lane + 32 * i;
-                if (d < hd) acc[i] += pj * to_f32(vr[d]);
+                if (d < vd) acc[i] += pj * to_f32(vr[d]);
             }
         }
     }
     const float inv = 1.f / l;
-    T* orow = out + (int64_t)t * n_heads * hd + (int64_t)h * hd;
+    T* orow = out + (int64_t)t * n_heads * vd + (int64_t)h * vd;
 #pragma unroll
     for (int i = 0; i < kMaxHd / 32; i++) {
         const int d = lane + 32 * i;
-        if (d < hd) orow[d] = from_f32<T>(acc[i] * inv);
+        if (d < vd) orow[d] = from_f32<T>(acc[i] * inv);
     }
 }
 
 }  // namespace
 
-// out [n, n_heads*hd]; q rows of n_heads*hd at stride q_stride (elements);
-// caches [pages, n_kv, page_size, hd]; block_table [requests, max_blocks].
+// out [n, n_heads*vd]; q rows of n_heads*hd at stride q_stride (elements);
+// caches [pages, n_kv, page_size, hd] and [pages, n_kv, page_size, vd]; block_table
+// [requests, max_blocks]; slopes optional float32 [n_heads].
 extern "C" int kllm_attention_generic(void* out, const void* q, int64_t q_stride,
                                       const void* kcache, const void* vcache,
                                       const int* positions, const int* token_req,
                                       const int* block_table, int max_blocks, int n_tokens,
-                                      int n_heads, int n_kv, int hd, int page_size, int window,
-                                      float scale, int dtype, void* stream) {
+                                      int n_heads, int n_kv, int hd, int vd, int page_size, int window,
+                                      float scale, const float* slopes, int dtype, void* stream) {
     if (n_tokens <= 0) return 0;
     if (hd <= 0 || hd > kMaxHd) KLLM_FAIL("attention: head size %d not in 1..%d", hd, kMaxHd);
+    if (vd <= 0 || vd > kMaxHd) KLLM_FAIL("attention: value size %d not in 1..%d", vd, kMaxHd);
     if (n_kv <= 0 || n_heads % n_kv) KLLM_FAIL("attention: %d heads over %d kv heads", n_heads, n_kv);
     if (page_size <= 0) KLLM_FAIL("attention: page size %d", page_size);
     cudaStream_t s = (cudaStream_t)stream;
@@ -113,13 +116,13 @@ extern "C" int kllm_attention_generic(void* out, const void* q, int64_t q_stride
     if (dtype == KLLM_F32)
         kllm_launch((attn_generic_kernel<float>), dim3(grid), dim3(kWarps * 32), 0, s, 
             (float*)out, (const float*)q, q_stride, (const float*)kcache, (const float*)vcache,
-            positions, token_req, block_table, max_blocks, n_tokens, n_heads, n_kv, hd, page_size,
-            window, scale);
+            positions, token_req, block_table, max_blocks, n_tokens, n_heads, n_kv, hd, vd, page_size,
+            window, scale, slopes);
     else if (dtype == KLLM_BF16)
         kllm_launch((attn_generic_kernel<bf16>), dim3(grid), dim3(kWarps * 32), 0, s, 
             (bf16*)out, (const bf16*)q, q_stride, (const bf16*)kcache, (const bf16*)vcache,
-            positions, token_req, block_table, max_blocks, n_tokens, n_heads, n_kv, hd, page_size,
-            window, scale);
+            positions, token_req, block_table, max_blocks, n_tokens, n_heads, n_kv, hd, vd, page_size,
+            window, scale, slopes);
     else
         KLLM_FAIL("attention: unknown element type %d", dtype);
     KLLM_LAUNCH_STATUS();

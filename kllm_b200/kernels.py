@@ -212,9 +212,14 @@ def rope_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cos_sin: Opti
 
 def attention_generic(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
                       positions: torch.Tensor, token_req: torch.Tensor, block_table: torch.Tensor,
-                      n_heads: int, n_kv: int, head_dim: int, window: int, scale: float) -> None:
-    """Causal GQA attention of every new token over its request's cached keys."""
-    _cuda(out, q, kcache, vcache, positions, token_req, block_table)
+                      n_heads: int, n_kv: int, head_dim: int, window: int, scale: float,
+                      score_slopes: Optional[torch.Tensor] = None, v_head_dim: Optional[int] = None) -> None:
+    """Causal GQA attention of every new token over its request's cached keys: one warp per
+    (token, head), any head size up to 256, values of their own size, optional score slopes."""
+    _cuda(out, q, kcache, vcache, positions, token_req, block_table, score_slopes)
+    vd = int(v_head_dim or head_dim)
+    if vcache.shape[3] != vd or vcache.shape[:3] != kcache.shape[:3] or out.shape[1] != n_heads * vd:
+        raise KernelError("attention: value cache [pages, n_kv, page_size, value size] and out [n, heads * value size]")
     _i32(positions, "positions"); _i32(token_req, "token_req"); _i32(block_table, "block_table")
     if q.stride(1) != 1 or not out.is_contiguous() or out.dtype != q.dtype or kcache.dtype != q.dtype:
         raise KernelError("attention: operands must share a dtype; out contiguous, q rows dense")
@@ -224,8 +229,9 @@ def attention_generic(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, 
     lib = load_library("attention_generic")
     rc = lib.kllm_attention_generic(_p(out), _p(q), ctypes.c_int64(q.stride(0)), _p(kcache), _p(vcache),
                                     _p(positions), _p(token_req), _p(block_table), block_table.shape[1],
-                                    n, n_heads, n_kv, head_dim, kcache.shape[2], int(window or 0),
-                                    ctypes.c_float(scale), dtype_code(q.dtype), _stream())
+                                    n, n_heads, n_kv, head_dim, vd, kcache.shape[2], int(window or 0),
+                                    ctypes.c_float(scale), _slopes_arg(score_slopes, n_heads), dtype_code(q.dtype),
+                                    _stream())
     _check(lib, "attention_generic", rc)
 
 
@@ -362,9 +368,9 @@ def attention(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: 
     tc = q.dtype == torch.bfloat16 and head_dim in TC_HEAD_DIMS and vd == head_dim and not (special and scale <= 0)
     if (special or vd != head_dim) and not (tc and group <= 64):
         if not simt_fits(q, n_heads, n_kv, head_dim, vd):
-            raise KernelError("attention: a bias on the scores, values of another size than the keys or float32 "
-                              "weights need head sizes that are multiples of 4 up to 256, at most 64 heads per kv "
-                              "head and rows aligned to four elements")
+            # head sizes that are no multiples of 4, very wide groups: one warp per (token, head)
+            return attention_generic(out, q, kcache, vcache, ctx.positions, ctx.token_req, block_table, n_heads, n_kv,
+                                     head_dim, window, scale, score_slopes, vd)
         return attention_simt(out, q, kcache, vcache, ctx, block_table, n_heads, n_kv, head_dim, window, scale,
                               score_slopes, vd)
     if tc and ctx.all_single and group <= 16:

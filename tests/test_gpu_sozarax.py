@@ -341,11 +341,15 @@ def _paged(k, v, page, n_pages, order_seed):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,G,dk,dv", [(4, 1, 96, 96), (4, 2, 16, 24), (6, 1, 8, 4), (2, 2, 32, 64)])
+@pytest.mark.parametrize("H,G,dk,dv", [(4, 1, 96, 96), (4, 2, 16, 24), (6, 1, 8, 4), (2, 2, 32, 64), (3, 1, 10, 6),
+                                       (8, 2, 64, 64), (40, 2, 16, 16)])
 def test_biased_attention_far_keys_and_page_borders(dtype, H, G, dk, dv):
     """One key far back is made to stand out (its score beats the distance bias); it sits just
     before or just after a page border, and the query is a prompt row or a single decoded token
-    whose context is cut into chunks.  Unused pages hold NaN."""
+    whose context is cut into chunks.  Unused pages hold NaN.  The shapes reach every kernel
+    that takes the bias: tensor cores (head sizes in steps of 16, values as wide as keys, in
+    bfloat16), the CUDA-core tiles (multiples of 4, values of their own size, float32), and one
+    warp per row (any size)."""
     import torch
     from kllm_b200 import kernels
     rng = np.random.default_rng(H * 100 + dk)
