@@ -207,10 +207,11 @@ expert_gemm_kernel(void* __restrict__ c_out, const T* __restrict__ a, int64_t a_
 }
 
 // ---- the same on the tensor cores, bfloat16 ---------------------------------------------------
-// 128 threads; warp w owns rows 16 w .. 16 w + 15 of the tile and all 64 columns.  A weight on
+// 256 threads: warp (wm, wn) = (w % 4, w / 4) owns MW 16-row tiles of the rows and columns 32 wn ..
+// 32 wn + 31 of the tile's 64.  A weight on
 // the expert's input is applied to the accumulators instead: W (s x) = s (W x), the same
 // number without rounding s x to bfloat16 first.
-constexpr int TN = 64, TK = 64, TLD = TK + 8, TSTAGES = 3, TT = 128;
+constexpr int TN = 64, TK = 64, TLD = TK + 8, TSTAGES = 3, TT = 256;
 
 __device__ __forceinline__ void cp16(bf16* dst, const bf16* src, bool ok) {
     const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
@@ -260,6 +261,7 @@ expert_gemm_mma_kernel(void* __restrict__ c_out, const bf16* __restrict__ a, int
     if (e >= E) return;
     const int r0 = lo + tile * TM, nr = min(TM, hi - r0), n0 = blockIdx.x * TN;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gid = lane >> 2, tq = lane & 3;
+    const int wm = warp & 3, wn = warp >> 2;
     for (int i = tid; i < TM; i += TT) {
         int src = 0, dst = 0;
         float sc = 1.f;
@@ -290,7 +292,7 @@ expert_gemm_mma_kernel(void* __restrict__ c_out, const bf16* __restrict__ a, int
                 cp16(&Bs[stage][b][cc][ch], we + (ok ? ((int64_t)b * N + n0 + cc) * K + k0 + ch : 0), ok);
             }
     };
-    float acc[NB][MW][8][4] = {};
+    float acc[NB][MW][4][4] = {};
     const int nk = (K + TK - 1) / TK;
 #pragma unroll
     for (int st = 0; st < TSTAGES - 1; st++) {
@@ -304,19 +306,19 @@ expert_gemm_mma_kernel(void* __restrict__ c_out, const bf16* __restrict__ a, int
         if (nxt < nk) load(nxt % TSTAGES, nxt * TK);
         asm volatile("cp.async.commit_group;\n" ::: "memory");
         const int st = it % TSTAGES;
-        if (16 * MW * warp >= nr) continue;                 // none of this warp's rows exists
+        if (16 * MW * wm >= nr) continue;                   // none of this warp's rows exists
 #pragma unroll
         for (int ks = 0; ks < TK / 16; ks++) {
             uint32_t af[MW][4];
 #pragma unroll
             for (int m = 0; m < MW; m++)
-                ldsm4(af[m], &As[st][16 * (MW * warp + m) + (lane & 15)][ks * 16 + (lane >> 4) * 8]);
+                ldsm4(af[m], &As[st][16 * (MW * wm + m) + (lane & 15)][ks * 16 + (lane >> 4) * 8]);
 #pragma unroll
             for (int b = 0; b < NB; b++)
 #pragma unroll
-                for (int np = 0; np < 4; np++) {
+                for (int np = 0; np < 2; np++) {
                     uint32_t bfr[4];
-                    ldsm4(bfr, &Bs[st][b][16 * np + (lane >> 4) * 8 + (lane & 7)][ks * 16 + ((lane >> 3) & 1) * 8]);
+                    ldsm4(bfr, &Bs[st][b][32 * wn + 16 * np + (lane >> 4) * 8 + (lane & 7)][ks * 16 + ((lane >> 3) & 1) * 8]);
 #pragma unroll
                     for (int m = 0; m < MW; m++) {
                         mma16816(acc[b][m][2 * np], af[m], bfr[0], bfr[1]);
@@ -330,14 +332,14 @@ expert_gemm_mma_kernel(void* __restrict__ c_out, const bf16* __restrict__ a, int
     for (int m = 0; m < MW; m++)
 #pragma unroll
         for (int h = 0; h < 2; h++) {
-            const int rr = 16 * (MW * warp + m) + gid + 8 * h;
+            const int rr = 16 * (MW * wm + m) + gid + 8 * h;
             if (rr >= nr) continue;
             const float sc = sscale[rr];
 #pragma unroll
-            for (int nt = 0; nt < 8; nt++)
+            for (int nt = 0; nt < 4; nt++)
 #pragma unroll
                 for (int j = 0; j < 2; j++) {
-                    const int cc = n0 + nt * 8 + 2 * tq + j;
+                    const int cc = n0 + 32 * wn + nt * 8 + 2 * tq + j;
                     if (cc >= N) continue;
                     if (GATED) {
                         const float gv = acc[0][m][nt][2 * h + j] * sc, uv = acc[NB - 1][m][nt][2 * h + j] * sc;

@@ -41,7 +41,20 @@ CFG_B = {
          "mlp": {"kind": "moe", "expert": {"ff": 12}, "router": {"experts": 5, "top": 1}}},
     ],
 }
-CFGS = {"A": (CFG_A, 11), "B": (CFG_B, 12)}
+# Sizes that fit no vector width, tile or tensor-core shape: every kernel's general form.
+CFG_C = {
+    "architecture": "Sozarax", "vocab": 61, "width": 50, "embedding": {"scale": 7.07}, "norm": {"eps": 1e-6},
+    "layers": [
+        {"type": "wkv", "mixer": {"heads": 2, "dim": 12, "decay_rank": 4},
+         "mlp": {"kind": "moe", "expert": {"ff": 7}, "router": {"experts": 2, "top": 1}}},
+        {"type": "attention", "mixer": {"heads": 3, "kv_heads": 1, "dim": 10, "vdim": 6, "scale": 0.4,
+                                        "q_temp": {"coef": 0.1, "every": 7}},
+         "mlp": {"kind": "dense", "ff": 13}},
+        {"type": "wkv", "mixer": {"heads": 5, "dim": 3, "decay_rank": 2}, "mlp": None},
+    ],
+    "loop": {"start": 0, "stop": 2, "times": 2},
+}
+CFGS = {"A": (CFG_A, 11), "B": (CFG_B, 12), "C": (CFG_C, 13)}
 # max |engine - plain| over a row, as a fraction of the largest |logit|.  float32: float32 sums
 # against float64 ones.  bfloat16: the plain implementation rounds nothing, so this is the whole
 # rounding of bfloat16 activations through the layers; a router's choice between two experts
@@ -92,7 +105,7 @@ def run_cut(eng, ids, cuts):
 # ---- whole models --------------------------------------------------------------------------
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_whole_prompt_and_every_way_of_cutting(tmp_path, name, dtype):
     cfg, w, d = make_model(tmp_path, name)
     rng = np.random.default_rng(5)

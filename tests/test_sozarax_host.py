@@ -26,7 +26,7 @@ def test_config_round_trip_and_refusals():
             parse_config(bad)
 
 
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_model_description(name):
     import torch
     import kllm_b200.models  # noqa: F401
