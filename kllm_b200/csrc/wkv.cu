@@ -14,7 +14,7 @@
 // that order whatever the batch holds and however the prompt was cut, and the state is
 // carried through the slot, so a position's result does not depend on the cutting.
 //
-// Three kernels:
+// Four kernels:
 //   shift_mix   m_s = h + (h_prev - h) * mu_s for s = 0 .. n_mix-1, h_prev being the row
 //               before in the same request, or the request's last row of the step before
 //               (kept in its state slot, zeros at the start); the slot is updated.
@@ -27,6 +27,7 @@
 //               up to 128: one CTA per (head, request), thread j owning all of S[.][j].
 //               In the slot the state lies as [heads][j][i], so a thread's part is
 //               contiguous and a warp's loads are whole lines.
+//   decay_outer z = W2 tanh(low): the outer half of the decay's low-rank product, tanh included.
 //   gate_norm   y = o / rms(o over the head's N values) * gain * silu(g).
 #include "common.cuh"
 
@@ -287,6 +288,45 @@ wkv_scan_split_kernel(float* __restrict__ o, int64_t o_stride, const float* __re
         *reinterpret_cast<float4*>(S_base + (int64_t)q * JQ * N) = make_float4(S[q][0], S[q][1], S[q][2], S[q][3]);
 }
 
+// ---- the decay's outer product: z[t, a] = sum_r tanh(low[t, r]) * W2[a, r] ---------------------
+// The inner width R is a handful (the decay's rank), far below what a matrix-product library is
+// made for: tanh(low) of a few rows in shared memory, float32 sums in the order r = 0 .. R-1.
+// A CTA has 256 channels a and up to DROWS rows t; a thread keeps eight weights of its channel
+// in registers at a time and serves all the CTA's rows with them.
+constexpr int DROWS = 16;
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+decay_outer_kernel(float* __restrict__ z, const float* __restrict__ low, int64_t low_stride, const T* __restrict__ w2,
+                   int n, int A, int R) {
+    extern __shared__ float th[];             // [DROWS][RP], RP = R rounded up to 8, zeros beyond R and beyond the rows
+    griddep_wait();
+    griddep_launch();
+    const int RP = (R + 7) & ~7;
+    const int t0 = blockIdx.y * DROWS, nt = min(DROWS, n - t0);
+    for (int i = threadIdx.x; i < DROWS * RP; i += blockDim.x) {
+        const int t = i / RP, r = i - t * RP;
+        th[i] = (t < nt && r < R) ? tanhf(low[(int64_t)(t0 + t) * low_stride + r]) : 0.f;
+    }
+    __syncthreads();
+    const int a = blockIdx.x * blockDim.x + threadIdx.x;
+    if (a >= A) return;
+    const T* wr = w2 + (int64_t)a * R;
+    float acc[DROWS];
+#pragma unroll
+    for (int t = 0; t < DROWS; t++) acc[t] = 0.f;
+    for (int r0 = 0; r0 < RP; r0 += 8) {
+        float w[8];
+#pragma unroll
+        for (int q = 0; q < 8; q++) w[q] = r0 + q < R ? to_f32(wr[r0 + q]) : 0.f;
+#pragma unroll
+        for (int t = 0; t < DROWS; t++)
+#pragma unroll
+            for (int q = 0; q < 8; q++) acc[t] += th[t * RP + r0 + q] * w[q];
+    }
+    for (int t = 0; t < nt; t++) z[(int64_t)(t0 + t) * A + a] = acc[t];
+}
+
 // ---- output: unit norm per head, gain, gate ---------------------------------------------
 // one warp per (token, head); lane l adds the squares of its channels l, l + 32, ... in that
 // order, then the lanes in a fixed tree.
@@ -337,19 +377,24 @@ extern "C" int kllm_wkv_shift_mix(void* out, const void* h, const float* mu, flo
 }
 
 // o, r, k, v, z float32 with `heads * N` dense columns and their own row strides; w0, u float32
-// [heads * N]; the state of request s is state[state_slots[s] * state_stride ..], [heads][N values][N keys].
+// [heads * N]; n_rows rows in all; the state of request s is state[state_slots[s] * state_stride ..], [heads][N values][N keys].
 extern "C" int kllm_wkv_scan(float* o, int64_t o_stride, const float* r, int64_t r_stride, const float* k,
                              int64_t k_stride, const float* v, int64_t v_stride, const float* z, int64_t z_stride,
                              const float* w0, const float* u, float* state, int64_t state_stride, const int* q_start,
-                             const int* state_slots, int n_requests, int heads, int N, void* stream) {
+                             const int* state_slots, int n_rows, int n_requests, int heads, int N, void* stream) {
     if (n_requests <= 0) return 0;
     if (heads <= 0 || N <= 0 || N > 128) KLLM_FAIL("wkv scan: %d heads of size %d (a head holds up to 128 channels)", heads, N);
     if (n_requests > 65535) KLLM_FAIL("wkv scan: %d requests in one launch", n_requests);
     cudaStream_t s = (cudaStream_t)stream;
+    // Over prompts it is not started early: the scan's few, long-running CTAs would be placed on
+    // whatever SMs the kernel before it has left free, two to an SM and others none, and run at
+    // that imbalance to their end (measured: 0.1 ms a layer over a 2048-row prompt).  Steps of
+    // a few rows per request (decode) gain from the early start like every short kernel.
+    const bool early = n_rows <= 4 * n_requests;
 #define KLLM_WKV_SPLIT_JT(IG, JT)                                                                                      \
     {                                                                                                                  \
         using C = WkvSplit<IG, JT>;                                                                                    \
-        kllm_launch((wkv_scan_split_kernel<IG, JT>), dim3(heads * (C::N / C::JB), n_requests), dim3(C::NTHR), 0, s, o, \
+        kllm_launch_dep(early, (wkv_scan_split_kernel<IG, JT>), dim3(heads * (C::N / C::JB), n_requests), dim3(C::NTHR), 0, s, o, \
                     o_stride, r, r_stride, k, k_stride, v, v_stride, z, z_stride, w0, u, state, state_stride, q_start, \
                     state_slots);                                                                                      \
         KLLM_LAUNCH_STATUS();                                                                                          \
@@ -366,13 +411,34 @@ extern "C" int kllm_wkv_scan(float* o, int64_t o_stride, const float* r, int64_t
 #undef KLLM_WKV_SPLIT_JT
 #undef KLLM_WKV_SPLIT
 #define KLLM_WKV(NMAX)                                                                                                  \
-    kllm_launch((wkv_scan_kernel<NMAX>), dim3(heads, n_requests), dim3(NMAX), 0, s, o, o_stride, r, r_stride, k, k_stride, \
+    kllm_launch_dep(early, (wkv_scan_kernel<NMAX>), dim3(heads, n_requests), dim3(NMAX), 0, s, o, o_stride, r, r_stride, k, k_stride, \
                 v, v_stride, z, z_stride, w0, u, state, state_stride, q_start, state_slots, N)
     if (N <= 32) KLLM_WKV(32);
     else if (N <= 64) KLLM_WKV(64);
     else if (N <= 96) KLLM_WKV(96);
     else KLLM_WKV(128);
 #undef KLLM_WKV
+    KLLM_LAUNCH_STATUS();
+}
+
+// z float32 [n][A] contiguous; low float32 [n][R] at row stride low_stride; w2 [A][R] contiguous in
+// the element type `dtype`.
+extern "C" int kllm_wkv_decay_outer(float* z, const float* low, int64_t low_stride, const void* w2, int n, int A, int R,
+                                    int dtype, void* stream) {
+    if (n <= 0) return 0;
+    if (A <= 0 || R <= 0) KLLM_FAIL("wkv decay: %d channels of rank %d", A, R);
+    cudaStream_t s = (cudaStream_t)stream;
+    const int row_tiles = (n + DROWS - 1) / DROWS;
+    if (row_tiles > 65535) KLLM_FAIL("wkv decay: %d rows in one launch", n);
+    const dim3 grid((A + 255) / 256, row_tiles);
+    const size_t smem = (size_t)DROWS * ((R + 7) & ~7) * sizeof(float);
+    if (smem > 48 * 1024) KLLM_FAIL("wkv decay: rank %d is beyond this kernel (use a matrix product)", R);
+    if (dtype == KLLM_F32)
+        kllm_launch((decay_outer_kernel<float>), grid, dim3(256), smem, s, z, low, low_stride, (const float*)w2, n, A, R);
+    else if (dtype == KLLM_BF16)
+        kllm_launch((decay_outer_kernel<bf16>), grid, dim3(256), smem, s, z, low, low_stride, (const bf16*)w2, n, A, R);
+    else
+        KLLM_FAIL("wkv decay: unknown element type %d", dtype);
     KLLM_LAUNCH_STATUS();
 }
 

@@ -977,9 +977,24 @@ def wkv_scan(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor,
     rc = lib.kllm_wkv_scan(_p(o), ctypes.c_int64(o.stride(0)), _p(r), ctypes.c_int64(r.stride(0)), _p(k),
                            ctypes.c_int64(k.stride(0)), _p(v), ctypes.c_int64(v.stride(0)), _p(z),
                            ctypes.c_int64(z.stride(0)), _p(w0), _p(u), _p(state), ctypes.c_int64(state.stride(0)),
-                           _p(ctx.q_start), _p(ctx.state_slots), ctx.n_requests, heads, size, _stream())
+                           _p(ctx.q_start), _p(ctx.state_slots), r.shape[0], ctx.n_requests, heads, size, _stream())
     _check(lib, "wkv", rc)
     return o
+
+
+def wkv_decay_outer(low: torch.Tensor, w2: torch.Tensor) -> torch.Tensor:
+    """z = tanh(low) @ w2^T in float32: low float32 [n, R] (the inner half of the decay's
+    low-rank product), w2 [A, R] in the model dtype; R is a handful."""
+    _cuda(low, w2)
+    n, R = low.shape
+    if low.dtype != torch.float32 or low.stride(1) != 1 or not w2.is_contiguous() or w2.shape[1] != R:
+        raise KernelError("wkv_decay_outer: low float32 [n, R] with dense rows, w2 contiguous [A, R]")
+    z = torch.empty((n, w2.shape[0]), dtype=torch.float32, device=low.device)
+    lib = load_library("wkv")
+    rc = lib.kllm_wkv_decay_outer(_p(z), _p(low), ctypes.c_int64(low.stride(0)), _p(w2), n, w2.shape[0], R,
+                                  dtype_code(w2.dtype), _stream())
+    _check(lib, "wkv", rc)
+    return z
 
 
 def wkv_gate_norm(o: torch.Tensor, g: torch.Tensor, gain: torch.Tensor, eps: float, heads: int, size: int,

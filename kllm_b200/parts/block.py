@@ -75,6 +75,17 @@ class PreNormBlock:
         return self.feed_forward.forward(xn, ctx)
 
 
+class DeferredNorm:
+    """What a block still owes the residual stream: ``x += norm(y)``.  Whoever runs next may fold
+    it into its own first norm (``norm.add_normed(x, y, then=...)``) or ``settle`` it."""
+
+    def __init__(self, norm, y):
+        self.norm, self.y = norm, y
+
+    def settle(self, x):
+        self.norm.add_normed(x, self.y)
+
+
 class SandwichNormBlock:
     """``sandwich_norm``: a norm before AND after each sublayer,
 
@@ -84,7 +95,12 @@ class SandwichNormBlock:
     ``mixer_post_norm`` and ``ff_post_norm`` (PartSpecs of the norm family whose parts offer
     ``add_normed``).  ``feed_forward`` may be None: the layer is its mixer alone.  The
     sublayers' outputs are float32; the norm behind the mixer and the norm in front of the
-    feed-forward are one kernel.  Nothing is ever pending."""
+    feed-forward are one kernel, and so are the norm behind the layer's last sublayer and the
+    first norm of the next block of this kind: the block hands on a ``DeferredNorm`` as its
+    ``pending`` (``accepts_deferred_norm``; the model settles it before a block that does not take
+    one, before its final norm, and for a debugging tap)."""
+
+    accepts_deferred_norm = True
 
     def __init__(self, spec: BlockSpec, env: BuildEnv):
         def norm(ps):
@@ -114,14 +130,15 @@ class SandwichNormBlock:
             p.bind(tensors)
 
     def forward(self, x, pending, ctx, cache):
-        xn = self.mixer_norm.forward(x, pending)
+        if isinstance(pending, DeferredNorm):
+            xn = pending.norm.add_normed(x, pending.y, then=self.mixer_norm)
+        else:
+            xn = self.mixer_norm.forward(x, pending)
         y = self.mixer.forward(xn, ctx, cache)
         if self.feed_forward is None:
-            self.mixer_post.add_normed(x, y)
-            return None
+            return DeferredNorm(self.mixer_post, y)
         xn = self.mixer_post.add_normed(x, y, then=self.ff_norm)
-        self.ff_post.add_normed(x, self.feed_forward.forward(xn, ctx))
-        return None
+        return DeferredNorm(self.ff_post, self.feed_forward.forward(xn, ctx))
 
 
 register_part("block", "pre_norm", PreNormBlock)

@@ -106,9 +106,16 @@ class DecoderModel:
             if cache.writes != call.writes_cache:
                 cache = LayerCache(cache.k, cache.v, cache.block_table, cache.state,
                                    writes=call.writes_cache, page_size=cache.page_size)
-            pending = self.blocks[call.block].forward(x, pending, ctx, cache)
+            block = self.blocks[call.block]
+            if hasattr(pending, "settle") and not getattr(block, "accepts_deferred_norm", False):
+                pending = pending.settle(x)
+            pending = block.forward(x, pending, ctx, cache)
             if self.tap is not None:
+                if hasattr(pending, "settle"):
+                    pending = pending.settle(x)
                 self.tap(i, x if pending is None else x + pending)
+        if hasattr(pending, "settle"):
+            pending = pending.settle(x)        # x += norm(y) of the last block
         if ctx.n_want == 0:
             return None
         if pending is None and hasattr(self.head, "forward_normed"):

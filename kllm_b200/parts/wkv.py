@@ -19,9 +19,10 @@ State (``StateNeed``): per request one float32 vector, [heads][value channel][ke
 S followed by [hidden] for the last row of h that the request has seen (rounded up to a
 multiple of four floats), zero when the request opens.
 Decay, state, sums, unit norm and gate are float32 in both dtypes; the projections take
-inputs in the model dtype and hand their results on unrounded (float32).  Kernels:
-csrc/wkv.cu (token shift, recurrence, unit norm and gate); the projections are library
-products.  A position's result does not depend on how its prompt was cut: the recurrence
+inputs in the model dtype and hand their results on unrounded (float32); the decay's inner
+product goes through tanh and its outer matrix in one float32 kernel.  Kernels: csrc/wkv.cu
+(token shift, decay, recurrence, unit norm and gate); the projections are library products,
+or the weight-streaming product for steps of a few rows.  A position's result does not depend on how its prompt was cut: the recurrence
 visits a request's rows one by one in order, whatever the batch.
 """
 from __future__ import annotations
@@ -65,7 +66,7 @@ class WkvMixer:
         self.mu = torch.stack([tensors[n[f"mu.{s}"]] for s in _MIX]).contiguous()
         # the four projections read four inputs: one batched product over the stacked matrices
         self.w_rkvg = torch.stack([tensors[n[s]] for s in ("r", "k", "v", "g")]).contiguous()
-        self.w1, self.w2 = tensors[n["w1"]], tensors[n["w2"]]
+        self.w1, self.w2 = tensors[n["w1"]], tensors[n["w2"]].contiguous()
         if self.w1.shape[0] != self.w2.shape[1]:
             raise ValueError(f"wkv: the decay's two matrices disagree on its rank ({tuple(self.w1.shape)}, "
                              f"{tuple(self.w2.shape)})")
@@ -86,8 +87,11 @@ class WkvMixer:
             r, k, v, g = (kernels.linear(mix[i], self.w_rkvg[i], out_dtype=f32, small_ok=True) for i in range(4))
         else:
             r, k, v, g = kernels.linear_batched(mix[:4], self.w_rkvg)
-        low = kernels.unary(kernels.linear(mix[4], self.w1, out_dtype=f32, small_ok=True), "tanh", self.dtype)
-        z = kernels.linear(low, self.w2, out_dtype=f32, small_ok=True)
+        low = kernels.linear(mix[4], self.w1, out_dtype=f32, small_ok=True)
+        if self.w2.shape[1] <= 256:
+            z = kernels.wkv_decay_outer(low, self.w2)           # tanh and the outer matrix in one kernel
+        else:
+            z = kernels.linear(kernels.unary(low, "tanh", self.dtype), self.w2, out_dtype=f32)
         o = kernels.wkv_scan(r, k, v, z, self.w0, self.u, state, ctx, self.heads, self.size)
         y = kernels.wkv_gate_norm(o, g, self.gain, self.eps, self.heads, self.size, self.dtype)
         return kernels.linear(y, self.w_o, out_dtype=f32, small_ok=True)

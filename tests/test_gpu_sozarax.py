@@ -331,6 +331,10 @@ def test_gate_norm_unary_and_post_norm():
     x = rng.standard_normal((n, 50))
     assert np.abs(kernels.unary(_t(x), "relu2", torch.float32).cpu().numpy() - np.maximum(x, 0) ** 2).max() <= 1e-6
     assert np.abs(kernels.unary(_t(x), "tanh", torch.float32).cpu().numpy() - np.tanh(x)).max() <= 1e-6
+    low, w2 = rng.standard_normal((n, 5)) * 2, P.round_bf16(rng.standard_normal((37, 5)))
+    for dt in ("float32", "bfloat16"):
+        z = kernels.wkv_decay_outer(_t(low), _t(w2, dt)).cpu().numpy()
+        assert np.abs(z - np.tanh(low) @ w2.T).max() <= 1e-5
     xs, ys, g1, g2 = rng.standard_normal((n, 50)), rng.standard_normal((n, 50)) * 4, rng.uniform(.5, 2, 50), rng.uniform(.5, 2, 50)
     xt, out = _t(xs), torch.empty((n, 50), device="cuda")
     kernels.rmsnorm_add(xt, _t(ys), _t(g1), 1e-6, out=out, gain2=_t(g2), eps2=1e-3)
