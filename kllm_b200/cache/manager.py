@@ -89,7 +89,8 @@ class CacheGroup:
     page_size: int
     pool: IdPool
     storage: Optional[torch.Tensor] = None   # [len(slots), 2, pages, kv heads, page_size, head_dim]; flat when the
-                                             # values have another size than the keys
+                                             # values have another size than the keys; without the 2 when the
+                                             # values are the keys (then v_store is k_store)
     k_store: Optional[torch.Tensor] = None   # [len(slots), pages, kv heads, page_size, head_dim]
     v_store: Optional[torch.Tensor] = None   # [len(slots), pages, kv heads, page_size, value size]
 
@@ -137,7 +138,7 @@ class CacheManager:
                 if isinstance(item, PagedKVNeed):
                     if item.window is not None and item.window <= 0:
                         raise ValueError(f"cache slot {slot}: window {item.window} must be positive")
-                    key = (item.n_kv_heads, item.head_dim, item.window, item.value_dim)
+                    key = (item.n_kv_heads, item.head_dim, item.window, item.value_dim, item.values_are_keys)
                     g = by_key.get(key)
                     if g is None:
                         g = CacheGroup(len(self.groups), item, [], page_size, IdPool(num_pages, "page"))
@@ -159,7 +160,10 @@ class CacheManager:
         if allocate:
             for g in self.groups:
                 L, G, hd, vd = len(g.slots), g.need.n_kv_heads, g.need.head_dim, g.need.value_dim
-                if vd == hd:
+                if g.need.values_are_keys:
+                    g.storage = torch.zeros((L, num_pages, G, page_size, hd), dtype=dtype, device=self.device)
+                    g.k_store = g.v_store = g.storage
+                elif vd == hd:
                     g.storage = torch.zeros((L, 2, num_pages, G, page_size, hd), dtype=dtype, device=self.device)
                     g.k_store, g.v_store = g.storage[:, 0], g.storage[:, 1]
                 else:
@@ -176,7 +180,7 @@ class CacheManager:
         """Device bytes that one more page in EVERY group's pool costs: keys and values of
         all layers of all groups (the pools have the same number of pages)."""
         esize = torch.empty((), dtype=self.dtype).element_size()
-        return sum(len(g.slots) * g.need.n_kv_heads * self.page_size * (g.need.head_dim + g.need.value_dim) * esize
+        return sum(len(g.slots) * g.need.n_kv_heads * self.page_size * g.need.stored_dim * esize
                    for g in self.groups)
 
     @classmethod
@@ -198,7 +202,7 @@ class CacheManager:
         """Cache bytes that one more token of context costs in the groups that keep
         every key."""
         esize = torch.empty((), dtype=self.dtype).element_size()
-        return sum(len(g.slots) * g.need.n_kv_heads * (g.need.head_dim + g.need.value_dim) * esize
+        return sum(len(g.slots) * g.need.n_kv_heads * g.need.stored_dim * esize
                    for g in self.groups if g.window is None)
 
     def pages_ever_needed(self, total_tokens: int) -> List[int]:

@@ -50,6 +50,25 @@ __global__ void silu_mul_vec4_kernel(bf16* __restrict__ out, int64_t out_stride,
     }
 }
 
+// out = act(gate, up) in the clamped form: g = min(gate, L), u = clamp(up, -L, L),
+// g * sigmoid(a g) * (u + 1); float32 gate and up rows at their strides.
+template <typename T>
+__global__ void clamped_glu_kernel(T* __restrict__ out, int64_t out_stride, const float* __restrict__ gate,
+                                   int64_t gate_stride, const float* __restrict__ up, int64_t up_stride, int n, int f,
+                                   float limit, float alpha) {
+    griddep_wait();
+    griddep_launch();
+    const int64_t total = (int64_t)n * f;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = idx / f;
+        const int c = (int)(idx - r * f);
+        const float g = fminf(gate[r * gate_stride + c], limit);
+        const float u = fminf(fmaxf(up[r * up_stride + c], -limit), limit);
+        out[r * out_stride + c] = from_f32<T>(g / (1.f + expf(-alpha * g)) * (u + 1.f));
+    }
+}
+
 // out = f(in) elementwise on float32 input rows: op 0 the square of relu, op 1 tanh.
 template <typename T>
 __global__ void unary_kernel(T* __restrict__ out, int64_t out_stride, const float* __restrict__ in, int64_t in_stride,
@@ -91,6 +110,25 @@ extern "C" int kllm_unary(void* out, int64_t out_stride, const void* in, int64_t
                     (const float*)in, in_stride, n, f, op);
     else
         KLLM_FAIL("unary: unknown element type %d", dtype);
+    KLLM_LAUNCH_STATUS();
+}
+
+// out [n][f] in the element type `dtype`; gate, up float32 [n][f]; dense rows at their strides.
+extern "C" int kllm_clamped_glu(void* out, int64_t out_stride, const float* gate, int64_t gate_stride, const float* up,
+                                int64_t up_stride, int n, int f, float limit, float alpha, int dtype, void* stream) {
+    if (n <= 0 || f <= 0) return 0;
+    if (!(limit > 0.f)) KLLM_FAIL("clamped glu: the limit must be positive");
+    cudaStream_t s = (cudaStream_t)stream;
+    int64_t blocks = ((int64_t)n * f + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (dtype == KLLM_F32)
+        kllm_launch((clamped_glu_kernel<float>), dim3((unsigned)blocks), dim3(256), 0, s, (float*)out, out_stride, gate,
+                    gate_stride, up, up_stride, n, f, limit, alpha);
+    else if (dtype == KLLM_BF16)
+        kllm_launch((clamped_glu_kernel<bf16>), dim3((unsigned)blocks), dim3(256), 0, s, (bf16*)out, out_stride, gate,
+                    gate_stride, up, up_stride, n, f, limit, alpha);
+    else
+        KLLM_FAIL("clamped glu: unknown element type %d", dtype);
     KLLM_LAUNCH_STATUS();
 }
 

@@ -1,7 +1,8 @@
 // Causal grouped-query attention over the paged cache, generic form: any head
-// size up to 256, values of their own size, any number of heads and kv heads, any query
+// size up to 512, values of their own size, any number of heads and kv heads, any query
 // length, an optional window, an optional bias on the scores that is linear in the distance
-// (slope[head] * (key position - query position)), float32 arithmetic throughout.  It is the whole attention of
+// (slope[head] * (key position - query position)), an optional sink per head (a term of the
+// softmax's denominator that has no key and no value), float32 arithmetic throughout.  It is the whole attention of
 // the float32 path and the fallback of the bfloat16 path for head sizes that the
 // tensor-core kernels do not take.
 //
@@ -21,7 +22,7 @@ KLLM_EXPORT_LAST_ERROR(attention_generic)
 namespace {
 
 constexpr int kWarps = 4;
-constexpr int kMaxHd = 256;
+constexpr int kMaxHd = 512;
 
 template <typename T>
 __global__ void __launch_bounds__(kWarps * 32)
@@ -30,7 +31,7 @@ attn_generic_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q_stri
                     const int* __restrict__ positions, const int* __restrict__ token_req,
                     const int* __restrict__ block_table, int max_blocks, int n_tokens,
                     int n_heads, int n_kv, int hd, int vd, int page_size, int window, float scale,
-                    const float* __restrict__ slopes) {
+                    const float* __restrict__ slopes, const float* __restrict__ sinks) {
     __shared__ float qs[kWarps][kMaxHd];
     griddep_wait();
     griddep_launch();
@@ -52,7 +53,8 @@ attn_generic_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q_stri
     float acc[kMaxHd / 32];
 #pragma unroll
     for (int i = 0; i < kMaxHd / 32; i++) acc[i] = 0.f;
-    float m = -INFINITY, l = 0.f;
+    // a sink: one more term exp(sink[h]) in the softmax's denominator, without a key or a value
+    float m = sinks ? sinks[h] : -INFINITY, l = sinks ? 1.f : 0.f;
 
     for (int base = start; base < len; base += 32) {
         const int key = base + lane;
@@ -98,13 +100,15 @@ attn_generic_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q_stri
 
 // out [n, n_heads*vd]; q rows of n_heads*hd at stride q_stride (elements);
 // caches [pages, n_kv, page_size, hd] and [pages, n_kv, page_size, vd]; block_table
-// [requests, max_blocks]; slopes optional float32 [n_heads].
+// [requests, max_blocks]; slopes optional float32 [n_heads]; sinks optional float32 [n_heads]:
+// exp(sinks[h]) is added to the denominator of head h's softmax (unscaled, once).
 extern "C" int kllm_attention_generic(void* out, const void* q, int64_t q_stride,
                                       const void* kcache, const void* vcache,
                                       const int* positions, const int* token_req,
                                       const int* block_table, int max_blocks, int n_tokens,
                                       int n_heads, int n_kv, int hd, int vd, int page_size, int window,
-                                      float scale, const float* slopes, int dtype, void* stream) {
+                                      float scale, const float* slopes, const float* sinks, int dtype,
+                                      void* stream) {
     if (n_tokens <= 0) return 0;
     if (hd <= 0 || hd > kMaxHd) KLLM_FAIL("attention: head size %d not in 1..%d", hd, kMaxHd);
     if (vd <= 0 || vd > kMaxHd) KLLM_FAIL("attention: value size %d not in 1..%d", vd, kMaxHd);
@@ -117,12 +121,12 @@ extern "C" int kllm_attention_generic(void* out, const void* q, int64_t q_stride
         kllm_launch((attn_generic_kernel<float>), dim3(grid), dim3(kWarps * 32), 0, s, 
             (float*)out, (const float*)q, q_stride, (const float*)kcache, (const float*)vcache,
             positions, token_req, block_table, max_blocks, n_tokens, n_heads, n_kv, hd, vd, page_size,
-            window, scale, slopes);
+            window, scale, slopes, sinks);
     else if (dtype == KLLM_BF16)
         kllm_launch((attn_generic_kernel<bf16>), dim3(grid), dim3(kWarps * 32), 0, s, 
             (bf16*)out, (const bf16*)q, q_stride, (const bf16*)kcache, (const bf16*)vcache,
             positions, token_req, block_table, max_blocks, n_tokens, n_heads, n_kv, hd, vd, page_size,
-            window, scale, slopes);
+            window, scale, slopes, sinks);
     else
         KLLM_FAIL("attention: unknown element type %d", dtype);
     KLLM_LAUNCH_STATUS();

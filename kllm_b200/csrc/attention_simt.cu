@@ -65,7 +65,7 @@ attn_simt_kernel(T* __restrict__ out, float* __restrict__ part_o, float* __restr
                  const T* __restrict__ vcache, const int* __restrict__ q_start, const int* __restrict__ start_pos,
                  const int* __restrict__ block_table, int max_blocks, int n_requests, int n_heads, int n_kv, int hd,
                  int vd, int page_size, int window, float scale, int qt, int chunk, int max_splits,
-                 const float* __restrict__ slopes) {
+                 const float* __restrict__ slopes, const float* __restrict__ sinks) {
     extern __shared__ __align__(16) float sm[];
     const int ld = hd + 4, ldv = vd + 4;
     float* Qs = sm;
@@ -129,9 +129,12 @@ attn_simt_kernel(T* __restrict__ out, float* __restrict__ part_o, float* __restr
     float4 acc[4][NC];
 #pragma unroll
     for (int i = 0; i < 4; i++) {
-        m[i] = -INFINITY;
-        l[i] = 0.f;
         const int r = ty + 16 * i;
+        // a sink is one more term exp(sink[h]) of the denominator, without key or value; where
+        // the keys are cut into chunks it joins the sum when the chunks are merged
+        const bool sunk = sinks && chunk == 0 && r < R;
+        m[i] = sunk ? sinks[g * gs + r % gs] : -INFINITY;
+        l[i] = sunk ? 1.f : 0.f;
         pos[i] = r < R ? p0 + r / gs : -1;                  // -1: no key is visible to a row that does not exist
         slope[i] = (slopes && r < R) ? slopes[g * gs + r % gs] : 0.f;
         wlo[i] = window > 0 ? pos[i] + 1 - window : 0;
@@ -503,7 +506,7 @@ template <typename T>
 __global__ void __launch_bounds__(128)
 attn_simt_merge_kernel(T* __restrict__ out, const float* __restrict__ part_o, const float* __restrict__ part_ml,
                        const int* __restrict__ positions, int n_rows, int n_heads, int hd, int window, int chunk,
-                       int max_splits) {
+                       int max_splits, const float* __restrict__ sinks) {
     griddep_wait();
     griddep_launch();
     const int lane = threadIdx.x & 31;
@@ -513,13 +516,14 @@ attn_simt_merge_kernel(T* __restrict__ out, const float* __restrict__ part_o, co
     const int lo_all = (window > 0 && p + 1 > window) ? p + 1 - window : 0;
     const int ns = (p + 1 - lo_all + chunk - 1) / chunk;
     // the chunks' maxima first (all loads at once), then their weights, then the sums in chunk order
-    float M = -INFINITY;
+    const float sink = sinks ? sinks[row % n_heads] : -INFINITY;
+    float M = sink;
     for (int j0 = 0; j0 < ns; j0 += 32) {
         const int j = j0 + lane;
         const float mj = j < ns ? __ldcg(part_ml + (row * max_splits + j) * 2) : -INFINITY;
         M = fmaxf(M, warp_max(mj));
     }
-    float L = 0.f;
+    float L = sinks ? expf(sink - M) : 0.f;
     float o[8];
 #pragma unroll
     for (int i = 0; i < 8; i++) o[i] = 0.f;
@@ -560,7 +564,7 @@ template <typename T, int NC>
 int launch(void* out, float* part_o, float* part_ml, const void* q, int64_t q_stride, const void* kcache,
            const void* vcache, const int* q_start, const int* start_pos, const int* block_table, int max_blocks,
            int n_requests, int max_tiles, int n_heads, int n_kv, int hd, int vd, int page_size, int window, float scale,
-           int qt, int chunk, int max_splits, const float* slopes, cudaStream_t s) {
+           int qt, int chunk, int max_splits, const float* slopes, const float* sinks, cudaStream_t s) {
     auto kern = attn_simt_kernel<T, NC>;
     static bool raised = false;
     const size_t smem = smem_bytes(hd, vd);
@@ -574,7 +578,7 @@ int launch(void* out, float* part_o, float* part_ml, const void* q, int64_t q_st
     }
     kllm_launch(kern, dim3(max_tiles * n_kv, 1, chunk > 0 ? max_splits : 1), dim3(THREADS), smem, s, (T*)out, part_o,
                 part_ml, (const T*)q, q_stride, (const T*)kcache, (const T*)vcache, q_start, start_pos, block_table,
-                max_blocks, n_requests, n_heads, n_kv, hd, vd, page_size, window, scale, qt, chunk, max_splits, slopes);
+                max_blocks, n_requests, n_heads, n_kv, hd, vd, page_size, window, scale, qt, chunk, max_splits, slopes, sinks);
     KLLM_LAUNCH_STATUS();
 }
 
@@ -590,12 +594,14 @@ int launch(void* out, float* part_o, float* part_ml, const void* q, int64_t q_st
 // max_splits of them, whose partial results go to part_o [rows, max_splits, vd] and
 // part_ml [rows, max_splits, 2] (row = token * n_heads + head) for kllm_attention_simt_merge.
 // slopes: optional float32 [n_heads]; slope[h] * (key position - query position) is added to
-// the scaled scores of head h.
+// the scaled scores of head h.  sinks: optional float32 [n_heads]; exp(sinks[h]) is added to the
+// denominator of head h's softmax (unscaled, once: with chunks, kllm_attention_simt_merge adds it).
 extern "C" int kllm_attention_simt(void* out, void* part_o, void* part_ml, const void* q, int64_t q_stride,
                                    const void* kcache, const void* vcache, const int* q_start, const int* start_pos,
                                    const int* block_table, int max_blocks, int n_requests, int max_tiles,
                                    int n_heads, int n_kv, int hd, int vd, int page_size, int window, float scale, int qt,
-                                   int chunk, int max_splits, const float* slopes, int dtype, void* stream) {
+                                   int chunk, int max_splits, const float* slopes, const float* sinks, int dtype,
+                                   void* stream) {
     if (n_requests <= 0 || max_tiles <= 0) return 0;
     if (hd <= 0 || hd > 256 || hd % 4) KLLM_FAIL("attention (simt): head size %d is not a multiple of 4 up to 256", hd);
     if (vd <= 0 || vd > 256 || vd % 4) KLLM_FAIL("attention (simt): value size %d is not a multiple of 4 up to 256", vd);
@@ -623,7 +629,7 @@ extern "C" int kllm_attention_simt(void* out, void* part_o, void* part_ml, const
 #define KLLM_SIMT(T, NC)                                                                                              \
     return launch<T, NC>(out, (float*)part_o, (float*)part_ml, q, q_stride, kcache, vcache, q_start, start_pos,      \
                          block_table, max_blocks, n_requests, max_tiles, n_heads, n_kv, hd, vd, page_size, window,    \
-                         scale, qt, chunk, max_splits, slopes, s)
+                         scale, qt, chunk, max_splits, slopes, sinks, s)
     if (dtype == KLLM_F32) {
         if (vd <= 64) KLLM_SIMT(float, 1);
         if (vd <= 128) KLLM_SIMT(float, 2);
@@ -639,17 +645,17 @@ extern "C" int kllm_attention_simt(void* out, void* part_o, void* part_ml, const
 
 extern "C" int kllm_attention_simt_merge(void* out, const void* part_o, const void* part_ml, const int* positions,
                                          int n_tokens, int n_heads, int hd, int window, int chunk, int max_splits,
-                                         int dtype, void* stream) {
+                                         const float* sinks, int dtype, void* stream) {
     if (n_tokens <= 0) return 0;
     if (hd <= 0 || hd > 256 || chunk <= 0 || max_splits < 1) KLLM_FAIL("attention merge (simt): bad sizes");
     cudaStream_t s = (cudaStream_t)stream;
     const int n_rows = n_tokens * n_heads;
     if (dtype == KLLM_F32)
         kllm_launch((attn_simt_merge_kernel<float>), dim3((n_rows + 3) / 4), dim3(128), 0, s, (float*)out,
-                    (const float*)part_o, (const float*)part_ml, positions, n_rows, n_heads, hd, window, chunk, max_splits);
+                    (const float*)part_o, (const float*)part_ml, positions, n_rows, n_heads, hd, window, chunk, max_splits, sinks);
     else if (dtype == KLLM_BF16)
         kllm_launch((attn_simt_merge_kernel<bf16>), dim3((n_rows + 3) / 4), dim3(128), 0, s, (bf16*)out,
-                    (const float*)part_o, (const float*)part_ml, positions, n_rows, n_heads, hd, window, chunk, max_splits);
+                    (const float*)part_o, (const float*)part_ml, positions, n_rows, n_heads, hd, window, chunk, max_splits, sinks);
     else
         KLLM_FAIL("attention merge (simt): unknown element type %d", dtype);
     KLLM_LAUNCH_STATUS();

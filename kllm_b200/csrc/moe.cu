@@ -15,7 +15,12 @@
 //             weight acts on the expert's input, and stores act(gate) * up per sorted row;
 //             "down" reads the sorted rows and stores row token * top + choice of a float32
 //             matrix, times the weight if it acts on the output.
-//   combine   y[t] = sum over the choices of a token, in choice order.
+//   combine   y[t] = sum over the choices of a token, in choice order; optionally plus the row of
+//             an expert that every token runs, times the sigmoid of a gate logit per token.
+//   table     instead of a router: a table [vocab][top] that gives every token id its experts,
+//             each with the same weight.
+// The gated activation is silu(g) * u, or with a limit L and a slope a the clamped form
+// min(g, L) * sigmoid(a min(g, L)) * (clamp(u, -L, L) + 1).
 //
 // A row's sums do not depend on which other rows share its tile or its launch.
 #include "common.cuh"
@@ -114,13 +119,26 @@ constexpr int BM = 32, BN = 64, BK = 32, GT = 256;
 
 __device__ __forceinline__ float act_silu(float g) { return g / (1.f + expf(-g)); }
 
+// The gated activation of an expert.  kind 0: silu(g) * u.  kind 1, with a limit L and a
+// slope a: g' = min(g, L), u' = clamp(u, -L, L), g' * sigmoid(a g') * (u' + 1).
+struct GatedAct {
+    int kind;
+    float limit, alpha;
+};
+__device__ __forceinline__ float gated_act(float g, float u, const GatedAct& a) {
+    if (a.kind == 0) return act_silu(g) * u;
+    g = fminf(g, a.limit);
+    u = fminf(fmaxf(u, -a.limit), a.limit);
+    return g / (1.f + expf(-a.alpha * g)) * (u + 1.f);
+}
+
 // GATED: W_e is [2 * N][K] (gate rows, then up rows), C [rows][N] in T, sorted order.
 // else : W_e is [N][K], C float32 [rows][N] at row perm[r].
 template <typename T, bool GATED>
 __global__ void __launch_bounds__(GT)
 expert_gemm_kernel(void* __restrict__ c_out, const T* __restrict__ a, int64_t a_stride, const T* __restrict__ w,
                    const int* __restrict__ offsets, const int* __restrict__ perm, const float* __restrict__ wt,
-                   int E, int top, int N, int K, int scale_in, int scale_out) {
+                   int E, int top, int N, int K, int scale_in, int scale_out, GatedAct act) {
     __shared__ float As[BK][BM + 1];
     __shared__ float Ws[GATED ? 2 : 1][BK][BN + 1];
     __shared__ int srow[BM];
@@ -198,7 +216,7 @@ expert_gemm_kernel(void* __restrict__ c_out, const T* __restrict__ a, int64_t a_
             const int cc = n0 + tx + 16 * j;
             if (cc >= N) continue;
             if (GATED) {
-                ((T*)c_out)[(int64_t)(r0 + rr) * N + cc] = from_f32<T>(act_silu(acc[0][i][j]) * acc[GATED ? 1 : 0][i][j]);
+                ((T*)c_out)[(int64_t)(r0 + rr) * N + cc] = from_f32<T>(gated_act(acc[0][i][j], acc[GATED ? 1 : 0][i][j], act));
             } else {
                 ((float*)c_out)[(int64_t)perm[r0 + rr] * N + cc] = acc[0][i][j] * sscale[rr];
             }
@@ -240,7 +258,7 @@ template <bool GATED, int MW>
 __global__ void __launch_bounds__(TT)
 expert_gemm_mma_kernel(void* __restrict__ c_out, const bf16* __restrict__ a, int64_t a_stride, const bf16* __restrict__ w,
                        const int* __restrict__ offsets, const int* __restrict__ perm, const float* __restrict__ wt,
-                       int E, int top, int N, int K, int scale_in, int scale_out) {
+                       int E, int top, int N, int K, int scale_in, int scale_out, GatedAct act) {
     constexpr int NB = GATED ? 2 : 1, TM = 64 * MW;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16 (*As)[TM][TLD] = reinterpret_cast<bf16 (*)[TM][TLD]>(smem_raw);                           // [TSTAGES]
@@ -343,7 +361,7 @@ expert_gemm_mma_kernel(void* __restrict__ c_out, const bf16* __restrict__ a, int
                     if (cc >= N) continue;
                     if (GATED) {
                         const float gv = acc[0][m][nt][2 * h + j] * sc, uv = acc[NB - 1][m][nt][2 * h + j] * sc;
-                        ((bf16*)c_out)[(int64_t)(r0 + rr) * N + cc] = __float2bfloat16_rn(act_silu(gv) * uv);
+                        ((bf16*)c_out)[(int64_t)(r0 + rr) * N + cc] = __float2bfloat16_rn(gated_act(gv, uv, act));
                     } else {
                         ((float*)c_out)[(int64_t)sdst[rr] * N + cc] = acc[0][m][nt][2 * h + j] * sc;
                     }
@@ -353,7 +371,8 @@ expert_gemm_mma_kernel(void* __restrict__ c_out, const bf16* __restrict__ a, int
 
 template <bool GATED, int MW>
 int launch_mma(void* c, const void* a, int64_t a_stride, const void* w, const int* offsets, const int* perm,
-               const float* wt, int rows, int E, int top, int N, int K, int scale_in, int scale_out, cudaStream_t s) {
+               const float* wt, int rows, int E, int top, int N, int K, int scale_in, int scale_out, GatedAct act,
+               cudaStream_t s) {
     auto kern = expert_gemm_mma_kernel<GATED, MW>;
     static bool raised = false;
     constexpr size_t smem = mma_smem_bytes<GATED, MW>();
@@ -368,12 +387,13 @@ int launch_mma(void* c, const void* a, int64_t a_stride, const void* w, const in
     const int row_tiles = (rows + 64 * MW - 1) / (64 * MW) + E;
     if (row_tiles > 65535) KLLM_FAIL("moe gemm: %d rows in one launch", rows);
     kllm_launch(kern, dim3((N + TN - 1) / TN, row_tiles), dim3(TT), smem, s, c, (const bf16*)a, a_stride, (const bf16*)w,
-                offsets, perm, wt, E, top, N, K, scale_in, scale_out);
+                offsets, perm, wt, E, top, N, K, scale_in, scale_out, act);
     KLLM_LAUNCH_STATUS();
 }
 
 __global__ void __launch_bounds__(256)
-combine_kernel(float* __restrict__ y, const float* __restrict__ parts, int64_t total, int d, int top) {
+combine_kernel(float* __restrict__ y, const float* __restrict__ parts, int64_t total, int d, int top,
+               const float* __restrict__ shared, const float* __restrict__ gate, int64_t gate_stride) {
     griddep_wait();
     griddep_launch();
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -381,8 +401,28 @@ combine_kernel(float* __restrict__ y, const float* __restrict__ parts, int64_t t
         const int c = (int)(i - t * d);
         float s = 0.f;
         for (int j = 0; j < top; j++) s += parts[(t * top + j) * d + c];
+        if (shared) s += shared[i] * (gate ? 1.f / (1.f + expf(-gate[t * gate_stride])) : 1.f);
         y[i] = s;
     }
+}
+
+// idx[t][j] = table[id of token t][j], wt = weight for every pair: experts that a table gives
+// a token by its id.  An id -(s + 1) stands for last_token[s], a choice of the step before that
+// is still on the device.
+__global__ void __launch_bounds__(256)
+table_route_kernel(int* __restrict__ idx, float* __restrict__ wt, const int* __restrict__ token_ids,
+                   const int* __restrict__ last_token, const int* __restrict__ table, int n, int vocab, int E, int top,
+                   float weight) {
+    griddep_wait();
+    griddep_launch();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n * top) return;
+    const int t = i / top, j = i - t * top;
+    int id = token_ids[t];
+    if (id < 0 && last_token) id = last_token[-id - 1];
+    id = min(max(id, 0), vocab - 1);
+    idx[i] = min(max(table[(int64_t)id * top + j], 0), E - 1);
+    wt[i] = weight;
 }
 
 }  // namespace
@@ -418,9 +458,12 @@ extern "C" int kllm_moe_sort(int* offsets, int* perm, int* rank, const int* idx,
 // gated == 0: a [rows][K] sorted, w [E][N][K], c float32 [rows][N] indexed by perm.
 extern "C" int kllm_moe_gemm(void* c, const void* a, int64_t a_stride, const void* w, const int* offsets,
                              const int* perm, const float* wt, int rows, int E, int top, int N, int K, int gated,
-                             int scale_in, int scale_out, int dtype, void* stream) {
+                             int scale_in, int scale_out, int act_kind, float act_limit, float act_alpha, int dtype,
+                             void* stream) {
     if (rows <= 0) return 0;
     if (N <= 0 || K <= 0 || E <= 0 || top <= 0) KLLM_FAIL("moe gemm: bad sizes");
+    if (act_kind < 0 || act_kind > 1) KLLM_FAIL("moe gemm: unknown activation %d", act_kind);
+    const GatedAct act = {act_kind, act_limit, act_alpha};
     const int row_tiles = (rows + BM - 1) / BM + E;
     if (row_tiles > 65535) KLLM_FAIL("moe gemm: %d rows in one launch", rows);
     cudaStream_t s = (cudaStream_t)stream;
@@ -429,7 +472,7 @@ extern "C" int kllm_moe_gemm(void* c, const void* a, int64_t a_stride, const voi
         // falls into changes no sum of that row)
         const bool tall = rows / E >= 128;
 #define KLLM_MOE_MMA(G, MW) \
-    return launch_mma<G, MW>(c, a, a_stride, w, offsets, perm, wt, rows, E, top, N, K, scale_in, scale_out, s)
+    return launch_mma<G, MW>(c, a, a_stride, w, offsets, perm, wt, rows, E, top, N, K, scale_in, scale_out, act, s)
         if (gated && tall) KLLM_MOE_MMA(true, 2);
         if (gated) KLLM_MOE_MMA(true, 1);
         if (tall) KLLM_MOE_MMA(false, 2);
@@ -439,7 +482,7 @@ extern "C" int kllm_moe_gemm(void* c, const void* a, int64_t a_stride, const voi
     const dim3 grid((N + BN - 1) / BN, row_tiles);
 #define KLLM_MOE(T, G)                                                                                            \
     kllm_launch((expert_gemm_kernel<T, G>), grid, dim3(GT), 0, s, c, (const T*)a, a_stride, (const T*)w, offsets, perm, \
-                wt, E, top, N, K, scale_in, scale_out)
+                wt, E, top, N, K, scale_in, scale_out, act)
     if (dtype == KLLM_F32) {
         if (gated) KLLM_MOE(float, true); else KLLM_MOE(float, false);
     } else if (dtype == KLLM_BF16) {
@@ -451,11 +494,25 @@ extern "C" int kllm_moe_gemm(void* c, const void* a, int64_t a_stride, const voi
     KLLM_LAUNCH_STATUS();
 }
 
-extern "C" int kllm_moe_combine(float* y, const float* parts, int n, int d, int top, void* stream) {
+// table int32 [vocab][top] with values in [0, E); token_ids int32 [n]; last_token optional.
+extern "C" int kllm_moe_table_route(int* idx, float* wt, const int* token_ids, const int* last_token, const int* table,
+                                    int n, int vocab, int E, int top, float weight, void* stream) {
+    if (n <= 0) return 0;
+    if (vocab <= 0 || E <= 0 || top <= 0 || top > E) KLLM_FAIL("moe table route: %d of %d experts, %d ids", top, E, vocab);
+    kllm_launch((table_route_kernel), dim3((n * top + 255) / 256), dim3(256), 0, (cudaStream_t)stream, idx, wt, token_ids,
+                last_token, table, n, vocab, E, top, weight);
+    KLLM_LAUNCH_STATUS();
+}
+
+// y[t] = sum of parts[t * top + j] over j in order (+ shared[t] * sigmoid(gate[t * gate_stride]) when
+// `shared` float32 [n][d] is given; gate NULL: the shared rows are added as they are).
+extern "C" int kllm_moe_combine(float* y, const float* parts, int n, int d, int top, const float* shared,
+                                const float* gate, int64_t gate_stride, void* stream) {
     if (n <= 0) return 0;
     const int64_t total = (int64_t)n * d;
     int64_t blocks = (total + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
-    kllm_launch((combine_kernel), dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, y, parts, total, d, top);
+    kllm_launch((combine_kernel), dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, y, parts, total, d, top,
+                shared, gate, gate_stride);
     KLLM_LAUNCH_STATUS();
 }

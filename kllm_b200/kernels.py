@@ -176,6 +176,62 @@ def qknorm_append(q_out: torch.Tensor, qkv: torch.Tensor, q_gain: torch.Tensor, 
     _check(lib, "qknorm_append", rc)
 
 
+def latent_norm_append(q_out: torch.Tensor, proj: torch.Tensor, q_gain: torch.Tensor, kv_gain: Optional[torch.Tensor],
+                       eps: float, positions: torch.Tensor, token_req: torch.Tensor,
+                       block_table: Optional[torch.Tensor], cache: Optional[torch.Tensor]) -> None:
+    """RMS norms of the two low-rank latents of a step's tokens (csrc/latent.cu): ``proj`` float32
+    [n, Rq + R] is the stacked down-projection's result; the query latent goes to ``q_out`` [n, Rq]
+    (model dtype), the key/value latent into the paged store ``cache`` [pages, 1, page_size, R] at
+    each token's position.  With ``cache`` None ``proj`` holds the query latents alone."""
+    _cuda(q_out, proj, q_gain, kv_gain, positions, token_req, block_table, cache)
+    _i32(positions, "positions"); _i32(token_req, "token_req"); _i32(block_table, "block_table")
+    n, Rq = q_out.shape
+    R = page_size = max_blocks = 0
+    if cache is not None:
+        R, page_size, max_blocks = cache.shape[3], cache.shape[2], block_table.shape[1]
+        if cache.dtype != q_out.dtype or not cache.is_contiguous() or cache.shape[1] != 1:
+            raise KernelError("latent_norm_append: the store must be contiguous [pages, 1, page_size, R] in q_out's dtype")
+        if kv_gain is None or kv_gain.dtype != torch.float32 or kv_gain.numel() != R or not kv_gain.is_contiguous():
+            raise KernelError("latent_norm_append: the key/value gain must be float32 [R]")
+    if proj.dtype != torch.float32 or proj.stride(1) != 1 or proj.shape != (n, Rq + R):
+        raise KernelError("latent_norm_append: the projections must be float32 [n, Rq + R] with dense rows")
+    if not q_out.is_contiguous() or q_gain.dtype != torch.float32 or q_gain.numel() != Rq or not q_gain.is_contiguous():
+        raise KernelError("latent_norm_append: q_out contiguous [n, Rq], the query gain float32 [Rq]")
+    lib = load_library("latent")
+    rc = lib.kllm_latent_norm_append(_p(q_out), _p(proj), ctypes.c_int64(proj.stride(0)), _p(q_gain), _p(kv_gain),
+                                     ctypes.c_float(eps), _p(positions), _p(token_req), _p(block_table), max_blocks,
+                                     _p(cache), n, Rq, R, page_size, dtype_code(q_out.dtype), _stream())
+    _check(lib, "latent", rc)
+
+
+def streams_step(streams: torch.Tensor, *, init: Optional[torch.Tensor] = None, y: Optional[torch.Tensor] = None,
+                 mix: Optional[torch.Tensor] = None, out_w: Optional[torch.Tensor] = None,
+                 in_w: Optional[torch.Tensor] = None, gain: Optional[torch.Tensor] = None, eps: float = 0.0,
+                 normed: Optional[torch.Tensor] = None, total: Optional[torch.Tensor] = None) -> None:
+    """One pass over S residual streams ``streams`` float32 [S, n, d] (csrc/streams.cu), in this
+    order: with ``init`` [n, d] the streams become S copies of it; with ``y`` [n, d] (a sublayer's
+    float32 output) every stream t becomes sum_s mix[s, t] x_s + out_w[t] y; with ``in_w`` [S] the
+    row sum_t in_w[t] x_t is RMS-normed with ``gain`` and stored in ``normed`` [n, d] (model
+    dtype); with ``total`` [n, d] the sum of the streams is stored there."""
+    _cuda(streams, init, y, mix, out_w, in_w, gain, normed, total)
+    if streams.dtype != torch.float32 or streams.dim() != 3 or not streams.is_contiguous():
+        raise KernelError("streams_step: the streams must be contiguous float32 [S, n, d]")
+    S, n, d = streams.shape
+    for t, shape, what in ((init, (n, d), "init"), (y, (n, d), "y"), (total, (n, d), "total"), (mix, (S, S), "mix"),
+                           (out_w, (S,), "out_w"), (in_w, (S,), "in_w"), (gain, (d,), "gain")):
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous() or tuple(t.shape) != shape):
+            raise KernelError(f"streams_step: {what} must be contiguous float32 {shape}")
+    if normed is not None and (not normed.is_contiguous() or tuple(normed.shape) != (n, d)):
+        raise KernelError("streams_step: normed must be contiguous [n, d]")
+    if (y is not None and (mix is None or out_w is None)) or (in_w is not None and (gain is None or normed is None)):
+        raise KernelError("streams_step: a write needs mix and out_w, a read needs gain and normed")
+    lib = load_library("streams")
+    rc = lib.kllm_streams_step(_p(streams), ctypes.c_int64(n * d), _p(init), _p(y), _p(mix), _p(out_w), _p(in_w),
+                               _p(gain), ctypes.c_float(eps), _p(normed), _p(total), n, d, S,
+                               dtype_code(normed.dtype if normed is not None else torch.float32), _stream())
+    _check(lib, "streams", rc)
+
+
 def rope_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cos_sin: Optional[torch.Tensor],
                 positions: torch.Tensor, token_req: torch.Tensor, block_table: Optional[torch.Tensor],
                 kcache: Optional[torch.Tensor], vcache: Optional[torch.Tensor],
@@ -213,10 +269,12 @@ def rope_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cos_sin: Opti
 def attention_generic(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
                       positions: torch.Tensor, token_req: torch.Tensor, block_table: torch.Tensor,
                       n_heads: int, n_kv: int, head_dim: int, window: int, scale: float,
-                      score_slopes: Optional[torch.Tensor] = None, v_head_dim: Optional[int] = None) -> None:
+                      score_slopes: Optional[torch.Tensor] = None, v_head_dim: Optional[int] = None,
+                      sinks: Optional[torch.Tensor] = None) -> None:
     """Causal GQA attention of every new token over its request's cached keys: one warp per
-    (token, head), any head size up to 256, values of their own size, optional score slopes."""
-    _cuda(out, q, kcache, vcache, positions, token_req, block_table, score_slopes)
+    (token, head), any head size up to 512, values of their own size, optional score slopes and
+    sinks (float32 [n_heads]: exp(sinks[h]) joins the denominator of head h's softmax)."""
+    _cuda(out, q, kcache, vcache, positions, token_req, block_table, score_slopes, sinks)
     vd = int(v_head_dim or head_dim)
     if vcache.shape[3] != vd or vcache.shape[:3] != kcache.shape[:3] or out.shape[1] != n_heads * vd:
         raise KernelError("attention: value cache [pages, n_kv, page_size, value size] and out [n, heads * value size]")
@@ -230,8 +288,8 @@ def attention_generic(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, 
     rc = lib.kllm_attention_generic(_p(out), _p(q), ctypes.c_int64(q.stride(0)), _p(kcache), _p(vcache),
                                     _p(positions), _p(token_req), _p(block_table), block_table.shape[1],
                                     n, n_heads, n_kv, head_dim, vd, kcache.shape[2], int(window or 0),
-                                    ctypes.c_float(scale), _slopes_arg(score_slopes, n_heads), dtype_code(q.dtype),
-                                    _stream())
+                                    ctypes.c_float(scale), _slopes_arg(score_slopes, n_heads),
+                                    _slopes_arg(sinks, n_heads, "sinks"), dtype_code(q.dtype), _stream())
     _check(lib, "attention_generic", rc)
 
 
@@ -240,7 +298,8 @@ SIMT_CHUNK = 256      # keys per CTA when a decoding token's context is cut (att
 
 def attention_simt(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, ctx,
                    block_table: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, window: int,
-                   scale: float, score_slopes: Optional[torch.Tensor] = None, v_head_dim: Optional[int] = None) -> None:
+                   scale: float, score_slopes: Optional[torch.Tensor] = None, v_head_dim: Optional[int] = None,
+                   sinks: Optional[torch.Tensor] = None) -> None:
     """Causal GQA attention of the step's tokens on the CUDA cores, float32 arithmetic
     (csrc/attention_simt.cu): the attention of the float32 path.  The requests that bring
     one token each at the head of the batch (decoding requests, which the scheduler puts
@@ -249,8 +308,10 @@ def attention_simt(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vca
     ``score_slopes`` (float32 [n_heads]): slope[h] * (key position - query position) is added
     to the scaled scores of head h.  ``v_head_dim``: the size of a head's values and of its
     output where it differs from the keys' (``vcache`` [pages, n_kv, page_size, v_head_dim],
-    ``out`` [n, n_heads * v_head_dim])."""
-    _cuda(out, q, kcache, vcache, block_table, score_slopes)
+    ``out`` [n, n_heads * v_head_dim]).  ``sinks`` (float32 [n_heads]): exp(sinks[h]) is one more
+    term of the denominator of head h's softmax, without a key or a value."""
+    _cuda(out, q, kcache, vcache, block_table, score_slopes, sinks)
+    _slopes_arg(sinks, n_heads, "sinks")
     vd = int(v_head_dim or head_dim)
     if score_slopes is not None and (score_slopes.dtype != torch.float32 or not score_slopes.is_contiguous()
                                      or score_slopes.numel() != n_heads):
@@ -281,10 +342,11 @@ def attention_simt(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vca
         rc = lib.kllm_attention_simt(_p(out), _p(part_o), _p(part_ml), _p(q), ctypes.c_int64(q.stride(0)), _p(kcache),
                                      _p(vcache), _p(ctx.q_start), _p(ctx.start_pos), _p(block_table),
                                      block_table.shape[1], singles, singles, *common, 1, SIMT_CHUNK, splits,
-                                     _p(score_slopes), dtype_code(q.dtype), _stream())
+                                     _p(score_slopes), _p(sinks), dtype_code(q.dtype), _stream())
         _check(lib, "attention_simt", rc)
         rc = lib.kllm_attention_simt_merge(_p(out), _p(part_o), _p(part_ml), _p(ctx.positions), singles, n_heads,
-                                           vd, int(window or 0), SIMT_CHUNK, splits, dtype_code(q.dtype), _stream())
+                                           vd, int(window or 0), SIMT_CHUNK, splits, _p(sinks), dtype_code(q.dtype),
+                                           _stream())
         _check(lib, "attention_simt", rc)
         first = singles
     if first < n_req:
@@ -293,7 +355,7 @@ def attention_simt(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vca
         rc = lib.kllm_attention_simt(_p(out), None, None, _p(q), ctypes.c_int64(q.stride(0)), _p(kcache), _p(vcache),
                                      _p(ctx.q_start[first:]), _p(ctx.start_pos[first:]), _p(block_table[first:]),
                                      block_table.shape[1], n_req - first, rest // qt + (n_req - first), *common, qt, 0, 1,
-                                     _p(score_slopes), dtype_code(q.dtype), _stream())
+                                     _p(score_slopes), _p(sinks), dtype_code(q.dtype), _stream())
         _check(lib, "attention_simt", rc)
 
 
@@ -345,7 +407,7 @@ def decode_splits(n_tokens: int, n_kv: int, ctx_bound: int) -> int:
 def attention(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, ctx,
               block_table: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, window: int,
               scale: float, score_slopes: Optional[torch.Tensor] = None, v_head_dim: Optional[int] = None,
-              exact_weights: bool = False) -> None:
+              exact_weights: bool = False, sinks: Optional[torch.Tensor] = None) -> None:
     """Causal GQA attention of the step's tokens over the paged cache, by the
     kernel that fits: bfloat16 with a head size in TC_HEAD_DIMS runs on tensor cores
     (the decode form when every request brings one token, else the prefill form: on
@@ -361,18 +423,21 @@ def attention(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: 
     ``exact_weights``: the softmax weights, computed in float32, must not meet the values
     rounded to one bfloat16: the ``mma.sync`` kernels then feed them to the tensor cores as
     two bfloat16 terms (16 bits of mantissa), the CUDA-core kernel as float32.  Values of
-    another size than the keys (``v_head_dim``) are taken by the CUDA-core kernel alone."""
+    another size than the keys (``v_head_dim``) are taken by the CUDA-core kernel alone.
+    ``sinks`` (float32 [n_heads]): exp(sinks[h]) joins the denominator of head h's softmax, a
+    term without a key or a value; taken by the CUDA-core kernels."""
     group = n_heads // max(1, n_kv)
     vd = int(v_head_dim or head_dim)
     special = score_slopes is not None or exact_weights
-    tc = q.dtype == torch.bfloat16 and head_dim in TC_HEAD_DIMS and vd == head_dim and not (special and scale <= 0)
-    if (special or vd != head_dim) and not (tc and group <= 64):
+    tc = (q.dtype == torch.bfloat16 and head_dim in TC_HEAD_DIMS and vd == head_dim and not (special and scale <= 0)
+          and sinks is None)
+    if (special or vd != head_dim or sinks is not None) and not (tc and group <= 64):
         if not simt_fits(q, n_heads, n_kv, head_dim, vd):
             # head sizes that are no multiples of 4, very wide groups: one warp per (token, head)
             return attention_generic(out, q, kcache, vcache, ctx.positions, ctx.token_req, block_table, n_heads, n_kv,
-                                     head_dim, window, scale, score_slopes, vd)
+                                     head_dim, window, scale, score_slopes, vd, sinks)
         return attention_simt(out, q, kcache, vcache, ctx, block_table, n_heads, n_kv, head_dim, window, scale,
-                              score_slopes, vd)
+                              score_slopes, vd, sinks)
     if tc and ctx.all_single and group <= 16:
         return attention_decode(out, q, kcache, vcache, ctx.positions, ctx.token_req, block_table, n_heads,
                                 n_kv, head_dim, window, scale,
@@ -415,9 +480,9 @@ def _check_attention(out, q, kcache, vcache, block_table, n_kv, head_dim):
     _i32(block_table, "block_table")
 
 
-def _slopes_arg(slopes, n_heads):
+def _slopes_arg(slopes, n_heads, what="score slopes"):
     if slopes is not None and (slopes.dtype != torch.float32 or not slopes.is_contiguous() or slopes.numel() != n_heads):
-        raise KernelError("attention: score slopes must be a contiguous float32 tensor, one per head")
+        raise KernelError(f"attention: {what} must be a contiguous float32 tensor, one per head")
     return _p(slopes)
 
 
@@ -610,6 +675,23 @@ def silu_mul(out: torch.Tensor, gate: torch.Tensor, up: torch.Tensor) -> None:
     rc = lib.kllm_silu_mul(_p(out), ctypes.c_int64(out.stride(0)), _p(gate), ctypes.c_int64(gate.stride(0)),
                            _p(up), ctypes.c_int64(up.stride(0)), n, f, dtype_code(out.dtype),
                            dtype_code(gate.dtype), _stream())
+    _check(lib, "activation", rc)
+
+
+def clamped_glu(out: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, limit: float, alpha: float) -> None:
+    """out = g * sigmoid(alpha g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit);
+    float32 gate and up with dense rows (strided rows allowed), out in float32 or bfloat16."""
+    _cuda(out, gate, up)
+    for t in (out, gate, up):
+        if t.stride(1) != 1:
+            raise KernelError("clamped_glu: operands must have dense rows")
+    if gate.dtype != torch.float32 or up.dtype != torch.float32 or gate.shape != out.shape or up.shape != out.shape:
+        raise KernelError("clamped_glu: gate and up must be float32 of out's shape")
+    n, f = out.shape
+    lib = load_library("activation")
+    rc = lib.kllm_clamped_glu(_p(out), ctypes.c_int64(out.stride(0)), _p(gate), ctypes.c_int64(gate.stride(0)),
+                              _p(up), ctypes.c_int64(up.stride(0)), n, f, ctypes.c_float(limit), ctypes.c_float(alpha),
+                              dtype_code(out.dtype), _stream())
     _check(lib, "activation", rc)
 
 
@@ -905,6 +987,26 @@ def linear_batched(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     return torch.stack([torch.mm(x[i], wt[i], out_dtype=torch.float32) for i in range(x.shape[0])])
 
 
+def linear_per_head(x: torch.Tensor, weight: torch.Tensor, transposed: bool = False) -> torch.Tensor:
+    """y[t, h, :] = weight[h] @ x[t, h, :] for every head h: x [n, H * a] contiguous, weight
+    [H, b, a] (``transposed``: weight [H, a, b], used as weight[h]^T), y [n, H * b] in x's dtype.
+    One batched product of the vendor GEMM library over the heads, reading x and writing y in
+    place at their head strides (bfloat16 operands accumulate in float32; float32 operands
+    run as true float32)."""
+    _cuda(x, weight)
+    if torch.backends.cuda.matmul.allow_tf32:
+        raise KernelError("TF32 matmul mode is on; the float32 path must stay true 32-bit")
+    n, H = x.shape[0], weight.shape[0]
+    a = weight.shape[1] if transposed else weight.shape[2]
+    b = weight.shape[2] if transposed else weight.shape[1]
+    if x.dtype != weight.dtype or not x.is_contiguous() or x.shape[1] != H * a:
+        raise KernelError("linear_per_head: x must be contiguous [n, heads * a] in the weights' dtype")
+    y = torch.empty((n, H * b), dtype=x.dtype, device=x.device)
+    torch.bmm(x.view(n, H, a).transpose(0, 1), weight if transposed else weight.transpose(1, 2),
+              out=y.view(n, H, b).transpose(0, 1))
+    return y
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None,
            out_dtype: Optional[torch.dtype] = None, small_ok: bool = False) -> torch.Tensor:
     """y = x @ weight^T through the vendor GEMM library (cuBLAS, via torch.mm), as
@@ -1032,6 +1134,8 @@ def unary(x: torch.Tensor, op: str, dtype: torch.dtype) -> torch.Tensor:
 
 # ---- routed experts (csrc/moe.cu) ------------------------------------------------------
 
+_GATED_ACT = {"silu": 0, "clamped": 1}
+
 def moe_route(h: torch.Tensor, router: torch.Tensor, top: int, score: str = "sigmoid", renormalize: bool = False):
     """(idx int32 [n, top], weights float32 [n, top]): logits router @ h in float32, scores by
     ``score`` ("sigmoid" or "softmax"), the ``top`` largest, the lower index among equals."""
@@ -1067,13 +1171,18 @@ def moe_sort(idx: torch.Tensor, experts: int):
 
 
 def moe_gemm(a: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, perm: torch.Tensor, wt: torch.Tensor, top: int,
-             gated: bool, scale_in: bool = False, scale_out: bool = False) -> torch.Tensor:
+             gated: bool, scale_in: bool = False, scale_out: bool = False, activation: str = "silu",
+             limit: float = 0.0, alpha: float = 1.0) -> torch.Tensor:
     """The experts' products over rows sorted by expert (``moe_sort``).  ``gated``: a is the
     layer's input [tokens, K], w [E, 2N, K] (gate rows, then up rows); returns silu(gate) * up
     [rows, N] in a's dtype, sorted order, the input row times its weight when ``scale_in``.
     Otherwise a is [rows, K] in sorted order, w [E, N, K]; returns float32 [rows, N] with row
-    token * top + choice, times its weight when ``scale_out``."""
+    token * top + choice, times its weight when ``scale_out``.  ``activation`` of the gated
+    form: "silu" (silu(g) * u) or "clamped" (with g' = min(g, limit) and u' = clamp(u, -limit,
+    limit): g' * sigmoid(alpha g') * (u' + 1))."""
     _cuda(a, w, offsets, perm, wt)
+    if activation not in _GATED_ACT or (activation == "clamped" and not limit > 0):
+        raise KernelError(f"moe_gemm: activation {activation!r} (silu, or clamped with a positive limit)")
     _i32(offsets, "offsets"); _i32(perm, "perm")
     rows = perm.numel()
     E, N, K = w.shape
@@ -1086,19 +1195,47 @@ def moe_gemm(a: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, perm: torc
     c = torch.empty((rows, N), dtype=a.dtype if gated else torch.float32, device=a.device)
     lib = load_library("moe")
     rc = lib.kllm_moe_gemm(_p(c), _p(a), ctypes.c_int64(a.stride(0)), _p(w), _p(offsets), _p(perm), _p(wt), rows, E,
-                           int(top), N, K, int(gated), int(scale_in), int(scale_out), dtype_code(a.dtype), _stream())
+                           int(top), N, K, int(gated), int(scale_in), int(scale_out), _GATED_ACT[activation],
+                           ctypes.c_float(limit), ctypes.c_float(alpha), dtype_code(a.dtype), _stream())
     _check(lib, "moe", rc)
     return c
 
 
-def moe_combine(parts: torch.Tensor, top: int) -> torch.Tensor:
-    """y[t] = sum of parts[t * top + j] over j in order; float32."""
-    _cuda(parts)
-    if top == 1:
+def moe_combine(parts: torch.Tensor, top: int, shared: Optional[torch.Tensor] = None,
+                gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y[t] = sum of parts[t * top + j] over j in order; float32.  With ``shared`` (float32
+    [n, d], the output of an expert that every token runs) also + shared[t] * sigmoid(gate[t]),
+    ``gate`` being a float32 column of one logit per token (None: the rows are added as they are)."""
+    _cuda(parts, shared, gate)
+    if top == 1 and shared is None:
         return parts
     n, d = parts.shape[0] // top, parts.shape[1]
+    if not parts.is_contiguous() or parts.dtype != torch.float32:
+        raise KernelError("moe_combine: the experts' rows must be contiguous float32")
+    if shared is not None and (shared.dtype != torch.float32 or not shared.is_contiguous() or shared.shape != (n, d)):
+        raise KernelError("moe_combine: the shared expert's rows must be contiguous float32 [n, d]")
+    if gate is not None and (shared is None or gate.dtype != torch.float32 or gate.dim() != 2 or gate.shape[0] != n):
+        raise KernelError("moe_combine: the gate is a float32 column [n, 1] beside a shared expert")
     y = torch.empty((n, d), dtype=torch.float32, device=parts.device)
     lib = load_library("moe")
-    rc = lib.kllm_moe_combine(_p(y), _p(parts), n, d, int(top), _stream())
+    rc = lib.kllm_moe_combine(_p(y), _p(parts), n, d, int(top), _p(shared), _p(gate),
+                              ctypes.c_int64(gate.stride(0) if gate is not None else 0), _stream())
     _check(lib, "moe", rc)
     return y
+
+
+def moe_table_route(token_ids: torch.Tensor, table: torch.Tensor, experts: int, weight: float,
+                    last_token: Optional[torch.Tensor] = None):
+    """(idx int32 [n, top], weights float32 [n, top]) from a table int32 [vocab, top] that gives
+    every token id its experts; every pair gets ``weight``.  An id -(s + 1) stands for
+    ``last_token[s]`` (a choice of the step before that is still on the device)."""
+    _cuda(token_ids, table, last_token)
+    _i32(token_ids, "token_ids"); _i32(table, "table"); _i32(last_token, "last_token")
+    n, (vocab, top) = token_ids.numel(), table.shape
+    idx = torch.empty((n, top), dtype=torch.int32, device=table.device)
+    wt = torch.empty((n, top), dtype=torch.float32, device=table.device)
+    lib = load_library("moe")
+    rc = lib.kllm_moe_table_route(_p(idx), _p(wt), _p(token_ids), _p(last_token), _p(table), n, vocab, int(experts),
+                                  top, ctypes.c_float(weight), _stream())
+    _check(lib, "moe", rc)
+    return idx, wt

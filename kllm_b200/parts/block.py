@@ -30,12 +30,14 @@ from .spec import BlockSpec, BuildEnv, part_factory, register_part
 class PreNormBlock:
     def __init__(self, spec: BlockSpec, env: BuildEnv):
         self.mixer = part_factory("mixer", spec.mixer.kind)(spec.mixer, env)
-        self.feed_forward = part_factory("feed_forward", spec.feed_forward.kind)(spec.feed_forward, env)
         self.mixer_norm = part_factory("norm", spec.mixer_norm.kind)(spec.mixer_norm, env)
-        self.ff_norm = part_factory("norm", spec.ff_norm.kind)(spec.ff_norm, env)
+        self.feed_forward = self.ff_norm = None            # a layer may be its mixer alone
+        if spec.feed_forward is not None:
+            self.feed_forward = part_factory("feed_forward", spec.feed_forward.kind)(spec.feed_forward, env)
+            self.ff_norm = part_factory("norm", spec.ff_norm.kind)(spec.ff_norm, env)
 
     def parts(self):
-        return [self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward]
+        return [p for p in (self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward) if p is not None]
 
     def tensor_specs(self):
         return [s for p in self.parts() for s in p.tensor_specs()]
@@ -68,6 +70,8 @@ class PreNormBlock:
         else:
             xn = self.mixer_norm.forward(x, pending)
             pending = self.mixer.forward(xn, ctx, cache)
+        if self.feed_forward is None:
+            return pending
         fused = getattr(self.feed_forward, "forward_residual", None)
         if pending is None and fused is not None and fused(x, self.ff_norm, ctx):
             return None
@@ -78,6 +82,8 @@ class PreNormBlock:
 class DeferredNorm:
     """What a block still owes the residual stream: ``x += norm(y)``.  Whoever runs next may fold
     it into its own first norm (``norm.add_normed(x, y, then=...)``) or ``settle`` it."""
+
+    accepted_by = "accepts_deferred_norm"      # the attribute by which a block says that it takes this hand-over
 
     def __init__(self, norm, y):
         self.norm, self.y = norm, y

@@ -1,0 +1,102 @@
+"""Attention through low-rank latents over a paged cache, without positions.
+
+    c_q = rmsnorm(W_dq h) * g_q          query latent, Rq values
+    c   = rmsnorm(W_dkv h) * g_kv        key/value latent, R values: the only thing cached
+    q_h = W_uq,h c_q;  k_h = W_uk,h c;  v_h = W_uv,h c        per head h
+    a_h = softmax_j( scale * q_h . k_h(j) )  over the keys j the query sees, with exp(sink_h)
+          as one more term of the denominator (no key, no value, not scaled)
+    out = W_o [a_1 v .. a_H v]
+
+The keys and values are never formed.  Since q_h . (W_uk,h c_j) = (W_uk,h^T q_h) . c_j, the
+queries are carried into the latent space (one small product per head) and the attention is
+that of H heads over ONE key/value head whose keys and values are both the cached rows c_j;
+its output, H rows of R values, goes through W_uv,h per head and then W_o.  The cache holds R
+values per token, [pages, 1, page_size, R], and the attention kernels read it as keys and as
+values (``PagedKVNeed.values_are_keys``).
+
+params: ``hidden``, ``n_heads``, ``head_dim`` (dk), ``v_head_dim`` (dv), ``q_rank`` (Rq),
+``kv_rank`` (R), ``scale``, ``eps`` (of both latent norms), ``window`` (None: every earlier
+key; W: the last W keys, the query's own included), ``cache_window`` (what the cache must
+keep: the widest window of all layers that read this cache; None: everything), ``sinks`` (True:
+a learned sink per head), ``own_latent`` (False: the layer reads the latents that another
+layer cached and has no W_dkv), ``tensors`` (dq, dq_norm, uq, dkv, dkv_norm, uk, uv, sink, o ->
+full names).
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from .spec import BuildEnv, PagedKVNeed, PartSpec, TensorSpec, register_part
+
+_NAMES = ("dq", "dq_norm", "uq", "dkv", "dkv_norm", "uk", "uv", "sink", "o")
+
+
+class LatentAttention:
+    def __init__(self, spec: PartSpec, env: BuildEnv):
+        p = spec.params
+        self.hidden = int(p["hidden"])
+        self.H, self.dk, self.dv = int(p["n_heads"]), int(p["head_dim"]), int(p["v_head_dim"])
+        self.Rq, self.R = int(p["q_rank"]), int(p["kv_rank"])
+        self.scale = float(p["scale"])
+        self.eps = float(p["eps"])
+        self.window = p.get("window")
+        self.cache_window = p.get("cache_window", self.window)
+        if self.cache_window is not None and (self.window is None or self.window > self.cache_window):
+            raise ValueError("latent attention: the cache keeps fewer keys than the layer's window sees")
+        self.has_sinks = bool(p.get("sinks", False))
+        self.own_latent = bool(p.get("own_latent", True))
+        names = dict(p.get("tensors") or {})
+        self.names = {k: names.get(k) or f"{spec.prefix}.{k}" for k in _NAMES}
+        self.dtype = env.dtype
+
+    def tensor_specs(self):
+        n, d, H = self.names, self.hidden, self.H
+        out = [TensorSpec(n["dq"], (self.Rq, d)),
+               TensorSpec(n["dq_norm"], (self.Rq,), store="float32", init="gain"),
+               TensorSpec(n["uq"], (H * self.dk, self.Rq)),
+               TensorSpec(n["uk"], (H * self.dk, self.R)),
+               TensorSpec(n["uv"], (H * self.dv, self.R)),
+               TensorSpec(n["o"], (d, H * self.dv))]
+        if self.own_latent:
+            out += [TensorSpec(n["dkv"], (self.R, d)),
+                    TensorSpec(n["dkv_norm"], (self.R,), store="float32", init="gain")]
+        if self.has_sinks:
+            out.append(TensorSpec(n["sink"], (H,), store="float32", init="zeros"))
+        return out
+
+    def bind(self, tensors):
+        n = self.names
+        self.w_dq = tensors[n["dq"]]
+        # both down-projections are one product
+        self.w_down = torch.cat([tensors[n["dq"]], tensors[n["dkv"]]], dim=0).contiguous() if self.own_latent else self.w_dq
+        self.g_q = tensors[n["dq_norm"]]
+        self.g_kv = tensors[n["dkv_norm"]] if self.own_latent else None
+        self.w_uq = tensors[n["uq"]]
+        self.w_uk = tensors[n["uk"]].view(self.H, self.dk, self.R)      # head h: [dk, R], q_h^T times it
+        self.w_uv = tensors[n["uv"]].view(self.H, self.dv, self.R)      # head h: [dv, R]
+        self.w_o = tensors[n["o"]]
+        self.sink = tensors[n["sink"]].contiguous() if self.has_sinks else None
+
+    def cache_need(self):
+        if not self.own_latent:
+            return None
+        return PagedKVNeed(1, self.R, self.cache_window, None, values_are_keys=True)
+
+    def forward(self, xn, ctx, cache):
+        n = xn.shape[0]
+        writes = cache.writes and self.own_latent
+        proj = kernels.linear(xn, self.w_down if writes else self.w_dq, out_dtype=torch.float32, small_ok=True)
+        cq = torch.empty((n, self.Rq), dtype=self.dtype, device=xn.device)
+        kernels.latent_norm_append(cq, proj, self.g_q, self.g_kv if writes else None, self.eps, ctx.positions,
+                                   ctx.token_req, cache.block_table if writes else None, cache.k if writes else None)
+        q = kernels.linear(cq, self.w_uq)
+        q_lat = kernels.linear_per_head(q, self.w_uk, transposed=True)                  # [n, H * R]
+        o_lat = torch.empty((n, self.H * self.R), dtype=self.dtype, device=xn.device)
+        kernels.attention(o_lat, q_lat, cache.k, cache.k, ctx, cache.block_table, self.H, 1, self.R,
+                          self.window or 0, self.scale, sinks=self.sink, exact_weights=True)
+        o = kernels.linear_per_head(o_lat, self.w_uv)                                    # [n, H * dv]
+        return kernels.linear(o, self.w_o, out_dtype=torch.float32, small_ok=True)
+
+
+register_part("mixer", "latent_attention", LatentAttention)

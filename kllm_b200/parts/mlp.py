@@ -1,6 +1,7 @@
 """Gated feed-forward (SwiGLU): down( act(x Wg^T) * (x Wu^T) ).
 
-params: ``hidden``, ``intermediate``, ``activation`` ("silu").  Tensors:
+params: ``hidden``, ``intermediate``, ``activation`` ("silu"), optional ``tensors`` (gate, up,
+down -> full names).  Tensors:
 ``<prefix>.{gate,up}_proj.weight`` [f, d] and ``<prefix>.down_proj.weight`` [d, f],
 no bias (reference backend/model.cu:1112-1115, activation :477-483).  Gate and up
 are stacked into one [2f, d] matrix at bind time so both are one product.
@@ -33,20 +34,21 @@ class GatedMLP:
         if self.activation != "silu":
             raise ValueError(f"gated feed-forward: activation {self.activation!r} has no kernel (silu only)")
         self.prefix = spec.prefix
+        names = dict(p.get("tensors") or {})
+        self.names = {k: names.get(k) or f"{self.prefix}.{k}_proj.weight" for k in ("gate", "up", "down")}
         self.dtype = env.dtype
         self.w_gate_up = None
         self.w_down = None
         self._after = []           # weights streamed right after this part (see set_prefetch_targets)
 
     def tensor_specs(self):
-        return [TensorSpec(f"{self.prefix}.gate_proj.weight", (self.inter, self.hidden)),
-                TensorSpec(f"{self.prefix}.up_proj.weight", (self.inter, self.hidden)),
-                TensorSpec(f"{self.prefix}.down_proj.weight", (self.hidden, self.inter))]
+        return [TensorSpec(self.names["gate"], (self.inter, self.hidden)),
+                TensorSpec(self.names["up"], (self.inter, self.hidden)),
+                TensorSpec(self.names["down"], (self.hidden, self.inter))]
 
     def bind(self, tensors):
-        self.w_gate_up = torch.cat([tensors[f"{self.prefix}.gate_proj.weight"],
-                                    tensors[f"{self.prefix}.up_proj.weight"]], dim=0).contiguous()
-        self.w_down = tensors[f"{self.prefix}.down_proj.weight"]
+        self.w_gate_up = torch.cat([tensors[self.names["gate"]], tensors[self.names["up"]]], dim=0).contiguous()
+        self.w_down = tensors[self.names["down"]]
 
     def streamed_weights(self):
         """The matrices this part streams in a small step, in kernel order."""

@@ -14,7 +14,8 @@ from typing import Dict, List, Optional
 import torch
 
 # registering the built-in part kinds
-from . import attention, block, embedding, mlp, moe, norm, qk_norm, rotary, wkv  # noqa: F401
+from . import (attention, block, embedding, latent_attention, mlp, moe, norm, qk_norm, rotary, streams,  # noqa: F401
+               wkv)
 from .context import LayerCache, StepContext
 from .spec import BuildEnv, ModelSpec, PagedKVNeed, StateNeed, TensorSpec, part_factory
 
@@ -107,13 +108,17 @@ class DecoderModel:
                 cache = LayerCache(cache.k, cache.v, cache.block_table, cache.state,
                                    writes=call.writes_cache, page_size=cache.page_size)
             block = self.blocks[call.block]
-            if hasattr(pending, "settle") and not getattr(block, "accepts_deferred_norm", False):
+            if hasattr(pending, "settle") and not getattr(block, getattr(pending, "accepted_by", "accepts_deferred_norm"),
+                                                           False):
                 pending = pending.settle(x)
             pending = block.forward(x, pending, ctx, cache)
             if self.tap is not None:
-                if hasattr(pending, "settle"):
-                    pending = pending.settle(x)
-                self.tap(i, x if pending is None else x + pending)
+                if hasattr(pending, "view"):
+                    self.tap(i, pending.view(x))       # what settle() would leave in x, without settling
+                else:
+                    if hasattr(pending, "settle"):
+                        pending = pending.settle(x)
+                    self.tap(i, x if pending is None else x + pending)
         if hasattr(pending, "settle"):
             pending = pending.settle(x)        # x += norm(y) of the last block
         if ctx.n_want == 0:

@@ -13,6 +13,19 @@ for the expert's number and matrix gate/up/down; default ``<prefix>.e{e}.{m}``).
 The router table stays float32 in both dtypes.  At bind time the experts' matrices are
 stacked into [E, 2f, d] (gate rows, then up rows) and [E, d, f].
 
+Further options, all absent by default:
+``routing`` "table": no router; an integer table ``table_tensor`` [vocab, top] gives every token
+id its experts (the entries of a row differ), each with the weight ``table_weight`` (default
+1 / top), applied where ``weight_on`` says.  The ids are the step's own (``ctx.token_ids``;
+an id that is still on the device from the step before is resolved there).
+``activation`` "clamped" with ``limit`` L and ``alpha`` a: the expert computes
+W_down (g sigmoid(a g) (u + 1)) with g = min(W_gate x, L), u = clamp(W_up x, -L, L) instead
+of silu(W_gate x) * (W_up x).
+``shared``: a dict {``ff``, ``activation``, ``limit``, ``alpha``, ``tensors`` (gate, up, down and
+optionally gate_logit -> full names)}: one more expert that every token runs, added to the
+routed ones, multiplied by sigmoid(w . x) when ``gate_logit`` names a [1, d] tensor.  Its gate,
+up and logit rows are one product; the sigmoid and the sum are part of the combine kernel.
+
 A step sorts its (token, choice) pairs by expert on the device and runs two grouped
 products over the sorted rows (csrc/moe.cu); shapes and launch sizes depend on the number
 of tokens alone, never on the routing, so decode steps can be replayed as CUDA graphs.
@@ -43,12 +56,45 @@ class RoutedExperts:
         self.router_name = p.get("router_tensor") or f"{spec.prefix}.router"
         self.fmt = p.get("expert_tensors") or (spec.prefix + ".e{e}.{m}")
         self.dtype = env.dtype
+        self.routing = p.get("routing", "scores")
+        if self.routing not in ("scores", "table"):
+            raise ValueError(f"routed experts: routing {self.routing!r} (scores, table)")
+        self.table_name = p.get("table_tensor") or f"{spec.prefix}.table"
+        self.table_weight = float(p.get("table_weight") or 1.0 / self.top)
+        self.table_vocab = int(p.get("vocab") or 0)
+        if self.routing == "table" and self.table_vocab <= 0:
+            raise ValueError("routed experts: a routing table needs the vocabulary's size ('vocab')")
+        self.act = self._activation(p)
+        sh = p.get("shared")
+        self.shared = None
+        if sh:
+            self.shared = {"ff": int(sh["ff"]), "act": self._activation(sh), "names": dict(sh["tensors"])}
+
+    @staticmethod
+    def _activation(p):
+        kind = p.get("activation", "silu")
+        if kind not in ("silu", "clamped"):
+            raise ValueError(f"routed experts: activation {kind!r} (silu, clamped)")
+        limit, alpha = float(p.get("limit") or 0.0), float(p.get("alpha") or 1.0)
+        if kind == "clamped" and not limit > 0:
+            raise ValueError("routed experts: the clamped activation needs a positive limit")
+        return {"activation": kind, "limit": limit, "alpha": alpha}
 
     def _name(self, e, m):
         return self.fmt.format(e=e, m=m)
 
     def tensor_specs(self):
-        out = [TensorSpec(self.router_name, (self.experts, self.hidden), store="float32")]
+        if self.routing == "table":
+            out = [TensorSpec(self.table_name, (self.table_vocab, self.top), store="int32",
+                              init=f"distinct:{self.experts}")]
+        else:
+            out = [TensorSpec(self.router_name, (self.experts, self.hidden), store="float32")]
+        if self.shared:
+            f, n = self.shared["ff"], self.shared["names"]
+            out += [TensorSpec(n["gate"], (f, self.hidden)), TensorSpec(n["up"], (f, self.hidden)),
+                    TensorSpec(n["down"], (self.hidden, f))]
+            if n.get("gate_logit"):
+                out.append(TensorSpec(n["gate_logit"], (1, self.hidden)))
         for e in range(self.experts):
             out += [TensorSpec(self._name(e, "gate"), (self.ff, self.hidden)),
                     TensorSpec(self._name(e, "up"), (self.ff, self.hidden)),
@@ -56,18 +102,42 @@ class RoutedExperts:
         return out
 
     def bind(self, tensors):
-        self.router = tensors[self.router_name]
+        self.router = tensors[self.router_name] if self.routing == "scores" else None
+        self.table = tensors[self.table_name].contiguous() if self.routing == "table" else None
+        if self.shared:
+            n = self.shared["names"]
+            rows = [tensors[n["gate"]], tensors[n["up"]]] + ([tensors[n["gate_logit"]]] if n.get("gate_logit") else [])
+            self.shared["w_in"] = torch.cat(rows, dim=0).contiguous()       # gate rows, up rows, the logit's row
+            self.shared["w_down"] = tensors[n["down"]]
         self.w_gate_up = torch.stack([torch.cat([tensors[self._name(e, "gate")], tensors[self._name(e, "up")]], dim=0)
                                       for e in range(self.experts)]).contiguous()
         self.w_down = torch.stack([tensors[self._name(e, "down")] for e in range(self.experts)]).contiguous()
 
+    def _shared(self, xn):
+        """(rows float32 [n, d], gate logits float32 [n, 1] or None) of the expert that every token runs."""
+        sh, f = self.shared, self.shared["ff"]
+        gu = kernels.linear(xn, sh["w_in"], out_dtype=torch.float32, small_ok=True)
+        act = torch.empty((xn.shape[0], f), dtype=self.dtype, device=xn.device)
+        if sh["act"]["activation"] == "clamped":
+            kernels.clamped_glu(act, gu[:, :f], gu[:, f:2 * f], sh["act"]["limit"], sh["act"]["alpha"])
+        else:
+            kernels.silu_mul(act, gu[:, :f], gu[:, f:2 * f])
+        rows = kernels.linear(act, sh["w_down"], out_dtype=torch.float32, small_ok=True)
+        return rows, (gu[:, 2 * f:] if gu.shape[1] > 2 * f else None)
+
     def forward(self, xn, ctx):
-        idx, wt = kernels.moe_route(xn, self.router, self.top, self.score, self.renormalize)
+        if self.routing == "table":
+            idx, wt = kernels.moe_table_route(ctx.token_ids, self.table, self.experts, self.table_weight, ctx.last_token)
+        else:
+            idx, wt = kernels.moe_route(xn, self.router, self.top, self.score, self.renormalize)
         offsets, perm = kernels.moe_sort(idx, self.experts)
         on_input = self.weight_on == "input"
-        act = kernels.moe_gemm(xn, self.w_gate_up, offsets, perm, wt, self.top, gated=True, scale_in=on_input)
+        act = kernels.moe_gemm(xn, self.w_gate_up, offsets, perm, wt, self.top, gated=True, scale_in=on_input, **self.act)
         parts = kernels.moe_gemm(act, self.w_down, offsets, perm, wt, self.top, gated=False, scale_out=not on_input)
-        return kernels.moe_combine(parts, self.top)
+        if self.shared is None:
+            return kernels.moe_combine(parts, self.top)
+        rows, logit = self._shared(xn)
+        return kernels.moe_combine(parts, self.top, shared=rows, gate=logit)
 
 
 register_part("feed_forward", "routed_experts", RoutedExperts)

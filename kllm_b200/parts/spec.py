@@ -26,7 +26,9 @@ class TensorSpec:
            "float32" -> kept in 32-bit whatever the model's dtype (norm gains,
            router tables); "int32" -> integer table.
     init:  how random-weights mode fills it: "normal" (mean 0), "gain" (mean 1),
-           "zeros", or "uniform:lo:hi"; the spreads are arguments of that mode.
+           "zeros", "uniform:lo:hi", "eye" (the identity), "mean" (1 / first size), or for an
+           integer table "distinct:B" (rows of different values below B); the spreads are
+           arguments of that mode.
     optional: may be absent from the files (the part then copes, e.g. a tied head).
     free:  indices of dimensions whose size the files decide (a rank that no configuration
            key names); ``shape`` then holds the size that random-weights mode draws, and the
@@ -90,15 +92,24 @@ class ModelSpec:
 class PagedKVNeed:
     """Keys and values in pages.  window None: every key is kept; window W: only
     the last W keys of a request are ever read, older pages may be given back.
-    v_head_dim: the size of a head's values where it differs from the keys' (None: the same)."""
+    v_head_dim: the size of a head's values where it differs from the keys' (None: the same).
+    values_are_keys: one row per token serves as key and as value (a layer that attends
+    through a cached low-rank latent): no value store is kept, the views of the values are the
+    keys'."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     v_head_dim: Optional[int] = None
+    values_are_keys: bool = False
 
     @property
     def value_dim(self) -> int:
         return self.v_head_dim or self.head_dim
+
+    @property
+    def stored_dim(self) -> int:
+        """Elements kept per token and kv head."""
+        return self.head_dim if self.values_are_keys else self.head_dim + self.value_dim
 
 
 @dataclass(frozen=True)

@@ -38,7 +38,16 @@ def random_tensor(spec, seed: int, std: float, gain_std: float, dtype: torch.dty
     if spec.init == "zeros":
         return torch.zeros(spec.shape, dtype=dtype, device=device)
     if spec.store == "int32":
+        if spec.init.startswith("distinct:") and len(spec.shape) == 2:
+            # every row holds different values below the bound: the first columns of a random permutation
+            bound = int(spec.init.split(":")[1])
+            keys = torch.rand((spec.shape[0], bound), generator=g, dtype=torch.float32, device=device)
+            return keys.argsort(dim=1)[:, :spec.shape[1]].to(torch.int32).contiguous()
         raise ValueError(f"random-weights mode cannot fill the integer table {spec.name}")
+    if spec.init == "eye":
+        return torch.eye(spec.shape[0], dtype=dtype, device=device)
+    if spec.init == "mean":
+        return torch.full(spec.shape, 1.0 / spec.shape[0], dtype=dtype, device=device)
     t = torch.randn(spec.shape, generator=g, dtype=torch.float32, device=device)
     if spec.init.startswith("uniform:"):
         lo, hi = (float(v) for v in spec.init.split(":")[1:])
