@@ -42,6 +42,8 @@ dense and routed feed-forwards) at two layer sizes beside a Llama of the same wi
 heads and feed-forward size: prefill and decode throughput of both models, and the design's
 own kernels one by one against their rooflines beside the Llama kernel that does the like
 work.  A record of its own; the default line does not change.
+``--design nutizen`` does the same for the Nutizen design (attention over cached low-rank
+latents in a window with sinks, several residual streams, experts assigned by a table).
 """
 from __future__ import annotations
 
@@ -248,8 +250,8 @@ def main():
     ap.add_argument("--workload", default="", choices=["", "llama2-7b-mixed"],
                     help="llama2-7b-mixed: 32 requests, prompts uniform in [128, 3072], 128 new tokens each, through "
                          "the scheduler (a record of its own, not the bench line)")
-    ap.add_argument("--design", default="", choices=["", "sozarax"],
-                    help="sozarax: prefill and decode of that design at two layer sizes beside a Llama of equal size, and "
+    ap.add_argument("--design", default="", choices=["", "sozarax", "nutizen"],
+                    help="sozarax, nutizen: prefill and decode of that design at two layer sizes beside a Llama of equal size, and "
                          "its kernels against their rooflines (a record of its own, not the bench line)")
     args = ap.parse_args()
     if args.timeline:
@@ -624,6 +626,35 @@ def sozarax_config(width, layers, heads, kv_heads, head_dim, ff, experts, top, e
             "layers": [{"type": t, "mixer": dict(m), "mlp": dict(f)} for t, m, f in (pattern[i % 4] for i in range(layers))]}
 
 
+def nutizen_config(width, layers, heads, head_dim, ff, experts, top, expert_ff, vocab, q_rank, kv_rank, window, streams):
+    """A Nutizen model of ``layers`` layers in the pattern dense, experts + shared expert, experts
+    (reading the latents of the layer before), dense; every head has ``head_dim`` query/key and
+    value channels."""
+    def mixer(src=None):
+        m = {"heads": heads, "dim": head_dim, "vdim": head_dim, "q_rank": q_rank, "kv_rank": kv_rank,
+             "scale": head_dim ** -0.5, "mask": {"size": window}}
+        if src is not None:
+            m["kv_from"] = src
+        return m
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff, "limit": 7.0}, "router": {"experts": experts, "top": top}}
+    out = []
+    for i in range(layers):
+        k = i % 4
+        out.append({"type": "latent_attention", "mixer": mixer(i - 1 if k == 2 else None),
+                    "mlp": dict(dense) if k in (0, 3) else dict(moe, shared={"ff": expert_ff, "limit": 7.0}) if k == 1
+                    else dict(moe)})
+    return {"architecture": "Nutizen", "vocab": vocab, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+            "streams": streams, "layers": out}
+
+
+NUTIZEN_EXTRA = {
+    # name: query latent, key/value latent, window, residual streams
+    "2048-wide": (768, 128, 1024, 4),
+    "4096-wide": (1536, 256, 1024, 4),
+}
+
+
 DESIGN_SIZES = {
     # name: width, layers, heads, kv heads, head size, dense ff, experts, top, expert ff, vocabulary
     "2048-wide": (2048, 8, 32, 4, 64, 5632, 8, 2, 1408, 32000),
@@ -818,8 +849,149 @@ def design_comparison(args):
             del wsets, dsets
         return rows
 
+    def nutizen_rows(width, heads, kv, hd, ff, E, top, eff, Rq, R, window, S):
+        """The Nutizen design's own kernels, each beside the Llama kernel that does the like work."""
+        rows = []
+        dev, f32 = "cuda", torch.float32
+        hbm, tens = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+        esz = 2 if dtype == "bfloat16" else 4
+
+        def note(name, us, bytes_=0, flops=0, like=None):
+            t_mem, t_flop = bytes_ / hbm * 1e6, flops / tens * 1e6
+            floor = max(t_mem, t_flop)
+            rows.append({"kernel": name, "us": round(us, 1), "floor_us": round(floor, 2),
+                         "bound": "memory" if t_mem >= t_flop else "tensor",
+                         "times_floor": round(us / floor, 1) if floor > 0 else None, "like": like})
+
+        def ctx_of(n_new, start):
+            import itertools
+            import types
+            Sq = len(n_new)
+            qs = torch.tensor([0] + list(itertools.accumulate(n_new)), dtype=torch.int32, device=dev)
+            return types.SimpleNamespace(
+                n_tokens=sum(n_new), n_requests=Sq, q_start=qs,
+                token_req=torch.repeat_interleave(torch.arange(Sq, dtype=torch.int32), torch.tensor(n_new)).to(dev),
+                start_pos=torch.tensor(start, dtype=torch.int32, device=dev),
+                positions=torch.cat([torch.arange(s, s + c, dtype=torch.int32) for s, c in zip(start, n_new)]).to(dev),
+                host_n_new=list(n_new), host_start_pos=list(start), all_single=all(c == 1 for c in n_new),
+                max_ctx=max(s + c for s, c in zip(start, n_new)), split_bound=0, max_new=max(n_new))
+
+        # ---- attention over the cached latents (window, sinks), and Llama's attention with the same window ----
+        for name, n_new, start in (("attention prefill", [T], [0]), ("attention decode", [1] * B, [ctx - 1] * B)):
+            c = ctx_of(n_new, start)
+            n, Sq = sum(n_new), len(n_new)
+            per = -(-max(s + m for s, m in zip(start, n_new)) // page)
+            table = torch.arange(Sq * per, dtype=torch.int32, device=dev).view(Sq, per).contiguous()
+            pairs = sum(min(p + 1, window) for s, m in zip(start, n_new) for p in range(s, s + m))
+            seen = sum(min(s + m, window + m - 1) for s, m in zip(start, n_new))        # cached rows that are read
+            it = [0]
+            stores = rotate(lambda: torch.randn(Sq * per, 1, page, R, device=dev).to(tdt), Sq * per * page * R * esz)
+            q = (torch.randn(n, heads * R, device=dev) * 0.1).to(tdt)
+            out = torch.empty_like(q)
+            sinks = torch.zeros(heads, device=dev)
+
+            def call():
+                i = it[0] = it[0] + 1
+                st = stores[i % len(stores)]
+                kernels.attention(out, q, st, st, c, table, heads, 1, R, window, hd ** -0.5, sinks=sinks, exact_weights=True)
+            us = timed(call, inner=4) * 1e3
+            note("latent " + name, us, seen * R * esz + 2 * n * heads * R * esz,
+                 4.0 * pairs * heads * R if dtype == "bfloat16" else 0, like="llama " + name)
+            del stores
+            caches = rotate(lambda: (torch.randn(Sq * per, kv, page, hd, device=dev).to(tdt),
+                                     torch.randn(Sq * per, kv, page, hd, device=dev).to(tdt)), 2 * Sq * per * kv * page * hd * esz)
+            q2 = (torch.randn(n, heads * hd, device=dev) * 0.2).to(tdt)
+            out2 = torch.empty_like(q2)
+
+            def call2():
+                i = it[0] = it[0] + 1
+                kc, vc = caches[i % len(caches)]
+                kernels.attention(out2, q2, kc, vc, c, table, heads, kv, hd, window, hd ** -0.5)
+            us = timed(call2, inner=4) * 1e3
+            note("llama " + name, us, seen * kv * hd * 2 * esz + 2 * n * heads * hd * esz,
+                 4.0 * pairs * heads * hd if dtype == "bfloat16" else 0)
+            del caches
+        # ---- the streams' pass (write, read, norm) beside Llama's residual sum and norm ----
+        for name, n in (("prefill", T), ("decode", B)):
+            xs = rotate(lambda: torch.randn(S, n, width, device=dev), S * n * width * 4)
+            y = torch.randn(n, width, device=dev)
+            mix, ow, iw = torch.eye(S, device=dev), torch.ones(S, device=dev), torch.full((S,), 1.0 / S, device=dev)
+            gain = torch.ones(width, device=dev)
+            normed = torch.empty(n, width, dtype=tdt, device=dev)
+            it = [0]
+
+            def call():
+                i = it[0] = it[0] + 1
+                kernels.streams_step(xs[i % len(xs)], y=y, mix=mix, out_w=ow, in_w=iw, gain=gain, eps=1e-6, normed=normed)
+            us = timed(call, inner=4) * 1e3
+            note(f"streams write+read+norm ({S} streams) {name}", us, (2 * S + 1) * n * width * 4 + n * width * esz,
+                 like=f"llama sum+norm {name}")
+            x1 = rotate(lambda: torch.randn(n, width, device=dev), n * width * 4)
+
+            def call2():
+                i = it[0] = it[0] + 1
+                kernels.add_rmsnorm(x1[i % len(x1)], y, normed, gain, 1e-6)
+            us = timed(call2, inner=4) * 1e3
+            note(f"llama sum+norm {name}", us, 3 * n * width * 4 + n * width * esz)
+            del xs, x1
+        # ---- the experts a table assigns, the shared expert and the sum; Llama's dense products ----
+        for name, n in (("prefill", T), ("decode", B)):
+            x = (torch.randn(n, width, device=dev) * 0.5).to(tdt)
+            ids = torch.randint(0, 32000, (n,), dtype=torch.int32, device=dev)
+            tab = torch.rand(32000, E, device=dev).argsort(dim=1)[:, :top].to(torch.int32).contiguous()
+            wsets = rotate(lambda: ((torch.randn(E, 2 * eff, width, device=dev) * 0.02).to(tdt),
+                                    (torch.randn(E, width, eff, device=dev) * 0.02).to(tdt)), 3 * E * eff * width * esz)
+            it = [0]
+
+            def experts():
+                i = it[0] = it[0] + 1
+                gu, dn = wsets[i % len(wsets)]
+                idx, wt = kernels.moe_table_route(ids, tab, E, 1.0 / top)
+                offsets, perm = kernels.moe_sort(idx, E)
+                act = kernels.moe_gemm(x, gu, offsets, perm, wt, top, gated=True, activation="clamped", limit=7.0, alpha=1.702)
+                kernels.moe_combine(kernels.moe_gemm(act, dn, offsets, perm, wt, top, gated=False, scale_out=True), top)
+            us = timed(experts, inner=2) * 1e3
+            used = min(E, n * top)
+            note(f"table experts ({top} of {E}) {name}", us, 3.0 * used * eff * width * esz,
+                 6.0 * n * top * eff * width if dtype == "bfloat16" else 0, like=f"llama gate/up/down {name}")
+            dsets = rotate(lambda: ((torch.randn(2 * ff, width, device=dev) * 0.02).to(tdt),
+                                    (torch.randn(width, ff, device=dev) * 0.02).to(tdt)), 3 * ff * width * esz)
+            resid = torch.zeros(n, width, device=dev)
+
+            def dense():
+                i = it[0] = it[0] + 1
+                gu, dn = dsets[i % len(dsets)]
+                if n <= 16 and dtype == "bfloat16":
+                    act = kernels.skinny_gemm(gu[:ff], weight_up=gu[ff:], x=x, epilogue="swiglu")
+                    kernels.skinny_gemm(dn, x=act, epilogue="add", out=resid)
+                else:
+                    yy = kernels.linear(x, gu, out_dtype=f32)
+                    act = torch.empty(n, ff, dtype=tdt, device=dev)
+                    kernels.silu_mul(act, yy[:, :ff], yy[:, ff:])
+                    kernels.linear_add(resid, act, dn)
+            us = timed(dense, inner=2) * 1e3
+            note(f"llama gate/up/down {name}", us, 3.0 * ff * width * esz, 6.0 * n * ff * width if dtype == "bfloat16" else 0)
+            del wsets, dsets
+        return rows
+
     sizes = {}
     for name, (width, layers, heads, kv, hd, ff, E, top, eff, vocab) in DESIGN_SIZES.items():
+        if args.design == "nutizen":
+            Rq, R, window, S = NUTIZEN_EXTRA[name]
+            nut = nutizen_config(width, layers, heads, hd, ff, E, top, eff, vocab, Rq, R, window, S)
+            llama = dict(TINYLLAMA, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads,
+                         num_key_value_heads=kv, head_dim=hd, intermediate_size=ff, vocab_size=vocab,
+                         max_position_embeddings=max(ctx, T))
+            print(f"[bench] {name}: Nutizen", file=sys.stderr, flush=True)
+            rec = {"layers": layers, "heads": heads, "head_dim": hd, "q_rank": Rq, "kv_rank": R, "window": window,
+                   "streams": S, "ff": ff, "experts": f"{top} of {E} x {eff} + shared", "nutizen": model_run(nut, vocab)}
+            print(f"[bench] {name}: Llama of equal size", file=sys.stderr, flush=True)
+            rec["llama"] = model_run(llama, vocab)
+            print(f"[bench] {name}: kernels", file=sys.stderr, flush=True)
+            rec["kernels"] = nutizen_rows(width, heads, kv, hd, ff, E, top, eff, Rq, R, window, S)
+            sizes[name] = rec
+            torch.cuda.empty_cache()
+            continue
         soz = sozarax_config(width, layers, heads, kv, hd, ff, E, top, eff, vocab)
         llama = dict(TINYLLAMA, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads,
                      num_key_value_heads=kv, head_dim=hd, intermediate_size=ff, vocab_size=vocab,
@@ -834,7 +1006,7 @@ def design_comparison(args):
         sizes[name] = rec
         torch.cuda.empty_cache()
     sampler.stop()
-    print(json.dumps({"partial": "Sozarax beside a Llama of equal size", "dtype": dtype, "prefill_tokens": T,
+    print(json.dumps({"partial": f"{args.design.capitalize()} beside a Llama of equal size", "dtype": dtype, "prefill_tokens": T,
                       "decode_batch": B, "decode_context": ctx, "data": "synthetic, random weights",
                       "peaks": pk, "clocks": sampler.summary(t_begin, time.time()), "sizes": sizes}))
     return 0

@@ -189,6 +189,9 @@ struct DecodeFusion {
     const float* slopes;
     float inv_scale;
     int split_p;
+    // a sink per head: exp(sinks[head]) is one more term of the softmax's denominator, without a
+    // key or a value (NULL: none); the first key range of a token counts it
+    const float* sinks;
 };
 
 // what rounding to bfloat16 leaves of x
@@ -486,6 +489,9 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
         float M = -INFINITY;
 #pragma unroll
         for (int w = 0; w < 4; w++) M = fmaxf(M, sm_m[w * 16 + r]);
+        // the sink in the units of the unscaled scores
+        const float sk = (fu.sinks && split == 0) ? fu.sinks[g * gs + r] * fu.inv_scale : -INFINITY;
+        M = fmaxf(M, sk);
         float L = 0.f, O = 0.f;
         if (M > -INFINITY) {
 #pragma unroll
@@ -494,6 +500,7 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
                 L += sm_l[w * 16 + r] * f;
                 O += sm_o[(w * 16 + r) * HD + d] * f;
             }
+            if (sk > -INFINITY) L += exp2f((sk - M) * scale_log2e);
         }
         const int h = g * gs + r;
         if (num_splits == 1) {
@@ -560,7 +567,8 @@ attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int64_t 
                     const int* __restrict__ q_start, const int* __restrict__ start_pos,
                     const int* __restrict__ block_table, int max_blocks, int n_requests, int n_heads,
                     int n_kv, int page_size, int window, float scale_log2e, int tokens_per_tile,
-                    const float* __restrict__ slopes, float inv_scale, int split_p) {
+                    const float* __restrict__ slopes, float inv_scale, int split_p,
+                    const float* __restrict__ sinks) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* smem = reinterpret_cast<bf16*>(smem_raw);
     __shared__ int s_req, s_tok0;
@@ -598,6 +606,7 @@ attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int64_t 
     int pr[MT][2], wr[MT][2];            // position of the row's token (-1: row unused), first visible key
     bool vr[MT][2];
     float sl_[MT][2];                    // the row's slope over the scale (0 without a bias)
+    float sk_[MT][2];                    // the row's sink over the scale (-inf without one)
     uint32_t qa[MT][KSTEPS][4];
     int64_t orow[MT][2];
 #pragma unroll
@@ -611,6 +620,7 @@ attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int64_t 
             pr[m][h] = vr[m][h] ? pos0 + tt : -1;
             wr[m][h] = (window > 0) ? pr[m][h] + 1 - window : 0;
             sl_[m][h] = (slopes && vr[m][h]) ? slopes[g * gs + hh] * inv_scale : 0.f;
+            sk_[m][h] = (sinks && vr[m][h]) ? sinks[g * gs + hh] * inv_scale : -INFINITY;
             qp[h] = q + (int64_t)(tok0 + tt) * q_stride + (int64_t)(g * gs + hh) * HD;
             orow[m][h] = (int64_t)(tok0 + tt) * n_heads * HD + (int64_t)(g * gs + hh) * HD;
         }
@@ -638,8 +648,11 @@ attn_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, int64_t 
         for (int i = 0; i < DTILES; i++)
 #pragma unroll
             for (int j = 0; j < 4; j++) o[m][i][j] = 0.f;
-        mx[m][0] = mx[m][1] = -INFINITY;
-        l[m][0] = l[m][1] = 0.f;
+        // a sink starts the running maximum and counts 1 in the sum (the sums are per lane and
+        // meet at the end: one lane of the row's four holds it)
+        mx[m][0] = sk_[m][0]; mx[m][1] = sk_[m][1];
+        l[m][0] = (tq == 0 && sk_[m][0] > -INFINITY) ? 1.f : 0.f;
+        l[m][1] = (tq == 0 && sk_[m][1] > -INFINITY) ? 1.f : 0.f;
     }
 
 #pragma unroll
@@ -834,16 +847,18 @@ extern "C" int kllm_attention_decode(void* out, void* part_o, void* part_ml, con
                                      const void* kcache, const void* vcache, const int* positions,
                                      const int* token_req, const int* block_table, int max_blocks,
                                      int n_tokens, int n_heads, int n_kv, int hd, int page_size, int window,
-                                     float scale, int num_splits, const float* slopes, int split_p, void* stream) {
+                                     float scale, int num_splits, const float* slopes, int split_p,
+                                     const float* sinks, void* stream) {
     if (n_tokens <= 0) return 0;
     int rc = check_common(n_heads, n_kv, hd, page_size, q, q_stride);
     if (rc) return rc;
     if (n_heads / n_kv > 16) KLLM_FAIL("attention decode: %d heads per kv head, at most 16", n_heads / n_kv);
     if (num_splits < 1 || (num_splits > 1 && (!part_o || !part_ml))) KLLM_FAIL("attention decode: bad split arguments");
-    if (slopes && !(scale > 0.f)) KLLM_FAIL("attention decode: a bias on the scores needs a positive scale");
+    if ((slopes || sinks) && !(scale > 0.f)) KLLM_FAIL("attention decode: a bias on the scores or a sink needs a positive scale");
     DecodeFusion extra{};
     extra.slopes = slopes;
-    extra.inv_scale = slopes ? 1.f / scale : 0.f;
+    extra.sinks = sinks;
+    extra.inv_scale = (slopes || sinks) ? 1.f / scale : 0.f;
     extra.split_p = split_p;
     if (n_tokens > 65535 || n_kv > 65535) KLLM_FAIL("attention decode: grid too large");
     if ((rc = set_attributes())) return rc;
@@ -964,7 +979,7 @@ extern "C" int kllm_attention_decode_static(void* out, const void* q, int64_t q_
     }
     return kllm_attention_decode(out, part_o, part_ml, q, q_stride, kcache, vcache, positions, token_req,
                                  block_table, max_blocks, n_tokens, n_heads, n_kv, hd, page_size, window, scale,
-                                 num_splits, nullptr, 0, stream);
+                                 num_splits, nullptr, 0, nullptr, stream);
 }
 
 // Prefill form: requests' portions q_start[s]..q_start[s+1] (prefix sums, [n_requests+1])
@@ -973,13 +988,13 @@ extern "C" int kllm_attention_prefill(void* out, const void* q, int64_t q_stride
                                       const void* vcache, const int* q_start, const int* start_pos,
                                       const int* block_table, int max_blocks, int n_tokens, int n_requests,
                                       int n_heads, int n_kv, int hd, int page_size, int window, float scale,
-                                      const float* slopes, int split_p, void* stream) {
+                                      const float* slopes, int split_p, const float* sinks, void* stream) {
     if (n_tokens <= 0) return 0;
     int rc = check_common(n_heads, n_kv, hd, page_size, q, q_stride);
     if (rc) return rc;
     const int gs = n_heads / n_kv;
     if (gs > 64) KLLM_FAIL("attention prefill: %d heads per kv head, at most 64", gs);
-    if (slopes && !(scale > 0.f)) KLLM_FAIL("attention prefill: a bias on the scores needs a positive scale");
+    if ((slopes || sinks) && !(scale > 0.f)) KLLM_FAIL("attention prefill: a bias on the scores or a sink needs a positive scale");
     if ((rc = set_attributes())) return rc;
     const int tpt = PRE_ROWS / gs;
     const int max_tiles = n_tokens / tpt + n_requests;          // >= sum of ceil(n_s / tpt)
@@ -988,6 +1003,6 @@ extern "C" int kllm_attention_prefill(void* out, const void* q, int64_t q_stride
     kllm_launch((attn_prefill_kernel), dim3(grid), dim3(THREADS), PRE_SMEM_BYTES, (cudaStream_t)stream, 
         (bf16*)out, (const bf16*)q, q_stride, (const bf16*)kcache, (const bf16*)vcache, q_start, start_pos,
         block_table, max_blocks, n_requests, n_heads, n_kv, page_size, window, sl2e, tpt, slopes,
-        slopes ? 1.f / scale : 0.f, split_p);
+        (slopes || sinks) ? 1.f / scale : 0.f, split_p, sinks);
     KLLM_LAUNCH_STATUS();
 }

@@ -425,13 +425,13 @@ def attention(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: 
     two bfloat16 terms (16 bits of mantissa), the CUDA-core kernel as float32.  Values of
     another size than the keys (``v_head_dim``) are taken by the CUDA-core kernel alone.
     ``sinks`` (float32 [n_heads]): exp(sinks[h]) joins the denominator of head h's softmax, a
-    term without a key or a value; taken by the CUDA-core kernels."""
+    term without a key or a value; taken by the CUDA-core kernels and the ``mma.sync`` kernels."""
     group = n_heads // max(1, n_kv)
     vd = int(v_head_dim or head_dim)
     special = score_slopes is not None or exact_weights
-    tc = (q.dtype == torch.bfloat16 and head_dim in TC_HEAD_DIMS and vd == head_dim and not (special and scale <= 0)
-          and sinks is None)
-    if (special or vd != head_dim or sinks is not None) and not (tc and group <= 64):
+    special = special or sinks is not None
+    tc = q.dtype == torch.bfloat16 and head_dim in TC_HEAD_DIMS and vd == head_dim and not (special and scale <= 0)
+    if (special or vd != head_dim) and not (tc and group <= 64):
         if not simt_fits(q, n_heads, n_kv, head_dim, vd):
             # head sizes that are no multiples of 4, very wide groups: one warp per (token, head)
             return attention_generic(out, q, kcache, vcache, ctx.positions, ctx.token_req, block_table, n_heads, n_kv,
@@ -441,8 +441,8 @@ def attention(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: 
     if tc and ctx.all_single and group <= 16:
         return attention_decode(out, q, kcache, vcache, ctx.positions, ctx.token_req, block_table, n_heads,
                                 n_kv, head_dim, window, scale,
-                                decode_splits(ctx.n_tokens, n_kv, ctx.split_bound or ctx.max_ctx),
-                                slopes=score_slopes, split_weights=exact_weights)
+                                decode_splits(ctx.n_tokens, n_kv, min(ctx.split_bound or ctx.max_ctx, window or (1 << 30))),
+                                slopes=score_slopes, split_weights=exact_weights, sinks=sinks)
     singles = 0
     if tc and group <= 16 and ctx.host_n_new:
         while singles < ctx.n_requests and ctx.host_n_new[singles] == 1:
@@ -451,7 +451,8 @@ def attention(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: 
         # token t of the first `singles` is request t: no token-to-request table needed
         attention_decode(out[:singles], q[:singles], kcache, vcache, ctx.positions[:singles], None,
                          block_table[:singles], n_heads, n_kv, head_dim, window, scale,
-                         decode_splits(singles, n_kv, ctx.max_ctx), slopes=score_slopes, split_weights=exact_weights)
+                         decode_splits(singles, n_kv, min(ctx.max_ctx, window or (1 << 30))), slopes=score_slopes,
+                         split_weights=exact_weights, sinks=sinks)
     q_start, start_pos, table, n_req = ctx.q_start, ctx.start_pos, block_table, ctx.n_requests
     if 0 < singles < ctx.n_requests:
         q_start, start_pos, table, n_req = q_start[singles:], start_pos[singles:], block_table[singles:], n_req - singles
@@ -463,7 +464,7 @@ def attention(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: 
     if tc and group <= 64:
         return attention_prefill(out, q, kcache, vcache, q_start, start_pos, table,
                                  n_req, n_heads, n_kv, head_dim, window, scale, slopes=score_slopes,
-                                 split_weights=exact_weights)
+                                 split_weights=exact_weights, sinks=sinks)
     if simt_fits(q, n_heads, n_kv, head_dim):
         return attention_simt(out, q, kcache, vcache, ctx, block_table, n_heads, n_kv, head_dim, window, scale)
     return attention_generic(out, q, kcache, vcache, ctx.positions, ctx.token_req, block_table, n_heads, n_kv,
@@ -488,12 +489,13 @@ def _slopes_arg(slopes, n_heads, what="score slopes"):
 
 def attention_decode(out, q, kcache, vcache, positions, token_req, block_table, n_heads, n_kv, head_dim,
                      window, scale, num_splits: int, slopes: Optional[torch.Tensor] = None,
-                     split_weights: bool = False) -> None:
+                     split_weights: bool = False, sinks: Optional[torch.Tensor] = None) -> None:
     """Tensor-core decode attention: every token attends on its own, its keys cut
     into ``num_splits`` ranges that are merged in a fixed order.  ``slopes`` (float32 [heads]):
     slope[h] * (key position - query position) is added to the scaled scores; ``split_weights``:
-    the probabilities enter the second product as two bfloat16 terms instead of one."""
-    _cuda(out, q, kcache, vcache, positions, token_req, block_table, slopes)
+    the probabilities enter the second product as two bfloat16 terms instead of one; ``sinks``
+    (float32 [heads]): exp(sinks[h]) joins the denominator of head h's softmax."""
+    _cuda(out, q, kcache, vcache, positions, token_req, block_table, slopes, sinks)
     _check_attention(out, q, kcache, vcache, block_table, n_kv, head_dim)
     _i32(positions, "positions"); _i32(token_req, "token_req")
     n = q.shape[0]
@@ -506,7 +508,7 @@ def attention_decode(out, q, kcache, vcache, positions, token_req, block_table, 
                                    _p(kcache), _p(vcache), _p(positions), _p(token_req), _p(block_table),
                                    block_table.shape[1], n, n_heads, n_kv, head_dim, kcache.shape[2],
                                    int(window or 0), ctypes.c_float(scale), int(num_splits), _slopes_arg(slopes, n_heads),
-                                   int(bool(split_weights)), _stream())
+                                   int(bool(split_weights)), _slopes_arg(sinks, n_heads, "sinks"), _stream())
     _check(lib, "attention_tc", rc)
     global launches
     if num_splits > 1:
@@ -549,11 +551,11 @@ def attention_decode_fused(out, q, k_new, v_new, cos_sin, kcache, vcache, positi
 
 def attention_prefill(out, q, kcache, vcache, q_start, start_pos, block_table, n_requests, n_heads, n_kv,
                       head_dim, window, scale, slopes: Optional[torch.Tensor] = None,
-                      split_weights: bool = False) -> None:
+                      split_weights: bool = False, sinks: Optional[torch.Tensor] = None) -> None:
     """Tensor-core attention of portions: request s brings rows q_start[s]..q_start[s+1]
-    that start at cache position start_pos[s].  ``slopes`` and ``split_weights`` as in
+    that start at cache position start_pos[s].  ``slopes``, ``split_weights`` and ``sinks`` as in
     ``attention_decode``."""
-    _cuda(out, q, kcache, vcache, q_start, start_pos, block_table, slopes)
+    _cuda(out, q, kcache, vcache, q_start, start_pos, block_table, slopes, sinks)
     _check_attention(out, q, kcache, vcache, block_table, n_kv, head_dim)
     _i32(q_start, "q_start"); _i32(start_pos, "start_pos")
     lib = load_library("attention_tc", {"KLLM_HD": head_dim})
@@ -561,7 +563,7 @@ def attention_prefill(out, q, kcache, vcache, q_start, start_pos, block_table, n
                                     _p(q_start), _p(start_pos), _p(block_table), block_table.shape[1],
                                     q.shape[0], int(n_requests), n_heads, n_kv, head_dim, kcache.shape[2],
                                     int(window or 0), ctypes.c_float(scale), _slopes_arg(slopes, n_heads),
-                                    int(bool(split_weights)), _stream())
+                                    int(bool(split_weights)), _slopes_arg(sinks, n_heads, "sinks"), _stream())
     _check(lib, "attention_tc", rc)
 
 

@@ -113,8 +113,8 @@ class DecoderModel:
                 pending = pending.settle(x)
             pending = block.forward(x, pending, ctx, cache)
             if self.tap is not None:
-                if hasattr(pending, "view"):
-                    self.tap(i, pending.view(x))       # what settle() would leave in x, without settling
+                if hasattr(pending, "peek"):
+                    self.tap(i, pending.peek(x))       # what settle() would leave in x, without settling
                 else:
                     if hasattr(pending, "settle"):
                         pending = pending.settle(x)

@@ -40,7 +40,7 @@ class ResidualStreams:
         self.y = None
         return None
 
-    def view(self, x):
+    def peek(self, x):
         """What ``settle`` would leave in x, computed on a copy."""
         total = torch.empty_like(x)
         kernels.streams_step(self.xs.clone(), y=self.y, mix=self.mix, out_w=self.out_w, total=total)

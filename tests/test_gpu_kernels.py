@@ -807,11 +807,11 @@ def test_kernels_refuse_what_they_cannot_take():
     x = torch.zeros(2, 8)
     with pytest.raises(kernels.KernelError, match="CUDA"):
         kernels.add_rmsnorm(x, None, x.clone(), torch.ones(8), 1e-5)
-    q = torch.zeros(1, 2 * 272, device="cuda")
-    kc = torch.zeros(1, 1, 4, 272, device="cuda")
+    q = torch.zeros(1, 2 * 528, device="cuda")
+    kc = torch.zeros(1, 1, 4, 528, device="cuda")
     z = torch.zeros(1, dtype=torch.int32, device="cuda")
     with pytest.raises(kernels.KernelError, match="head size"):
-        kernels.attention_generic(torch.empty_like(q), q, kc, kc, z, z, z.view(1, 1), 2, 1, 272, 0, 1.0)
+        kernels.attention_generic(torch.empty_like(q), q, kc, kc, z, z, z.view(1, 1), 2, 1, 528, 0, 1.0)
     with pytest.raises(kernels.KernelError, match="float32 or bfloat16"):
         kernels.silu_mul(torch.zeros(1, 4, device="cuda", dtype=torch.float16),
                          torch.zeros(1, 4, device="cuda", dtype=torch.float16),
