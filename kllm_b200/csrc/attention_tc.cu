@@ -1,6 +1,7 @@
 // Causal grouped-query attention over the paged cache on tensor cores, bfloat16
 // operands with float32 accumulation, one library per head size (compiled with
-// -DKLLM_HD=<head size>, a multiple of 16 up to 128).
+// -DKLLM_HD=<head size>, a multiple of 16 up to 256; above 128 a thread's accumulators fill its
+// registers and three stages of tiles fill the shared memory: one CTA per SM).
 //
 // Two kernels share the tile loader and the softmax recurrence:
 //
@@ -48,7 +49,7 @@ KLLM_EXPORT_LAST_ERROR(attention_tc)
 namespace {
 
 constexpr int HD = KLLM_HD;
-static_assert(HD % 16 == 0 && HD >= 16 && HD <= 128, "head size must be a multiple of 16 up to 128");
+static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size must be a multiple of 16 up to 256");
 constexpr int KSTEPS = HD / 16;          // MMA k-steps over the head dims (scores)
 constexpr int DTILES = HD / 8;           // 8-wide output tiles over the head dims
 constexpr int CHUNKS = HD / 8;           // 16-byte pieces of a key row

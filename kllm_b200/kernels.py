@@ -369,6 +369,7 @@ def simt_fits(q: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, v_head_di
 
 
 TC_HEAD_DIMS = tuple(range(16, 129, 16))     # head sizes of the tensor-core attention library
+TC_WIDE_HEAD_DIMS = (160, 192, 224, 256)     # ... and those that only its unfused kernels are built for
 TCGEN05_HEAD_DIMS = (64, 128)                # head sizes of the tcgen05 prefill attention
 PREFETCH_L2 = os.environ.get("KLLM_B200_PREFETCH", "1") != "0"   # kernels warm L2 for the kernel after them
 # ... with at most this much of the next matrix: what is asked for beyond a fraction of the
@@ -430,7 +431,8 @@ def attention(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: 
     vd = int(v_head_dim or head_dim)
     special = score_slopes is not None or exact_weights
     special = special or sinks is not None
-    tc = q.dtype == torch.bfloat16 and head_dim in TC_HEAD_DIMS and vd == head_dim and not (special and scale <= 0)
+    tc = (q.dtype == torch.bfloat16 and (head_dim in TC_HEAD_DIMS or head_dim in TC_WIDE_HEAD_DIMS) and vd == head_dim
+          and not (special and scale <= 0))
     if (special or vd != head_dim) and not (tc and group <= 64):
         if not simt_fits(q, n_heads, n_kv, head_dim, vd):
             # head sizes that are no multiples of 4, very wide groups: one warp per (token, head)

@@ -242,7 +242,7 @@ def latent_heads_attention(q, c, H, R, scale, window, sink):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,R,window", [(4, 32, 64), (3, 48, 300), (8, 128, 0), (5, 10, 33), (2, 6, 7), (72, 16, 40),
-                                        (2, 320, 50)])
+                                        (2, 320, 50), (4, 256, 100), (20, 192, 0), (3, 144, 20)])
 def test_sink_attention_far_keys_window_edges_and_page_borders(dtype, H, R, window):
     """The last query looks for one key: far back, just before or after a page border, the first
     key its window keeps (distance window - 1) or the one just outside (distance window), which
