@@ -193,6 +193,11 @@ struct DecodeFusion {
     // a sink per head: exp(sinks[head]) is one more term of the softmax's denominator, without a
     // key or a value (NULL: none); the first key range of a token counts it
     const float* sinks;
+    // head groups per kv head (0 or 1: one).  A CTA's 16 rows hold the heads of one group; where
+    // more than 16 heads share a kv head the launcher cuts them into `share` groups and passes
+    // n_kv * share as the kernel's n_kv: the cache is then addressed with kv head g / share of
+    // n_kv / share, everything else goes by group.
+    int share;
 };
 
 // what rounding to bfloat16 leaves of x
@@ -281,6 +286,8 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
     if (!FUSED) { griddep_wait(); griddep_launch(); }
     const int split = blockIdx.x, g = blockIdx.y, t = blockIdx.z;
     const int gs = n_heads / n_kv;
+    const int share = fu.share > 1 ? fu.share : 1;
+    const int gk = g / share, nkc = n_kv / share;          // the kv head and their number, as the cache has them
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tq = lane & 3;
     const bool whole_row = !token_req && max_blocks <= DEC_PAGES;
     const int* table = block_table + (int64_t)(token_req ? token_req[t] : t) * max_blocks;
@@ -316,7 +323,7 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
     // the tiles do not depend on the query: start them first
 #pragma unroll
     for (int s = 0; s < DEC_STAGES - 1; s++) {
-        if (s < ntiles) load_tile(smem + s * STAGE_ELEMS, kcache, vcache, pages, lo + s * TILE, hi, g, n_kv, page_size, page_base);
+        if (s < ntiles) load_tile(smem + s * STAGE_ELEMS, kcache, vcache, pages, lo + s * TILE, hi, gk, nkc, page_size, page_base);
         cp_async_commit();
     }
     if (FUSED) l2_prefetch_slice(fu.prefetch, fu.prefetch_bytes, THREADS);   // after this kernel's own requests
@@ -406,7 +413,7 @@ attn_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float* __
         __syncthreads();
         const int nxt = i + DEC_STAGES - 1;
         if (nxt < ntiles)
-            load_tile(smem + (nxt % DEC_STAGES) * STAGE_ELEMS, kcache, vcache, pages, lo + nxt * TILE, hi, g, n_kv, page_size, page_base);
+            load_tile(smem + (nxt % DEC_STAGES) * STAGE_ELEMS, kcache, vcache, pages, lo + nxt * TILE, hi, gk, nkc, page_size, page_base);
         cp_async_commit();
         bf16* sk = smem + (i % DEC_STAGES) * STAGE_ELEMS;
         bf16* sv = sk + TILE * ROW;
@@ -853,10 +860,14 @@ extern "C" int kllm_attention_decode(void* out, void* part_o, void* part_ml, con
     if (n_tokens <= 0) return 0;
     int rc = check_common(n_heads, n_kv, hd, page_size, q, q_stride);
     if (rc) return rc;
-    if (n_heads / n_kv > 16) KLLM_FAIL("attention decode: %d heads per kv head, at most 16", n_heads / n_kv);
+    // more than 16 heads on a kv head: the fewest groups of equal size that fit a CTA's 16 rows
+    int share = 1;
+    while ((n_heads / n_kv) % share || (n_heads / n_kv) / share > 16) share++;
     if (num_splits < 1 || (num_splits > 1 && (!part_o || !part_ml))) KLLM_FAIL("attention decode: bad split arguments");
     if ((slopes || sinks) && !(scale > 0.f)) KLLM_FAIL("attention decode: a bias on the scores or a sink needs a positive scale");
     DecodeFusion extra{};
+    extra.share = share;
+    n_kv *= share;
     extra.slopes = slopes;
     extra.sinks = sinks;
     extra.inv_scale = (slopes || sinks) ? 1.f / scale : 0.f;

@@ -440,20 +440,22 @@ def attention(out: torch.Tensor, q: torch.Tensor, kcache: torch.Tensor, vcache: 
                                      head_dim, window, scale, score_slopes, vd, sinks)
         return attention_simt(out, q, kcache, vcache, ctx, block_table, n_heads, n_kv, head_dim, window, scale,
                               score_slopes, vd, sinks)
-    if tc and ctx.all_single and group <= 16:
+    # the decode kernel takes 16 heads per CTA: more heads on a kv head are cut into groups of equal size
+    groups = n_kv * next(s for s in range(1, group + 1) if group % s == 0 and group // s <= 16)
+    if tc and ctx.all_single and group <= 64:
         return attention_decode(out, q, kcache, vcache, ctx.positions, ctx.token_req, block_table, n_heads,
                                 n_kv, head_dim, window, scale,
-                                decode_splits(ctx.n_tokens, n_kv, min(ctx.split_bound or ctx.max_ctx, window or (1 << 30))),
+                                decode_splits(ctx.n_tokens, groups, min(ctx.split_bound or ctx.max_ctx, window or (1 << 30))),
                                 slopes=score_slopes, split_weights=exact_weights, sinks=sinks)
     singles = 0
-    if tc and group <= 16 and ctx.host_n_new:
+    if tc and group <= 64 and ctx.host_n_new:
         while singles < ctx.n_requests and ctx.host_n_new[singles] == 1:
             singles += 1
     if 0 < singles < ctx.n_requests:
         # token t of the first `singles` is request t: no token-to-request table needed
         attention_decode(out[:singles], q[:singles], kcache, vcache, ctx.positions[:singles], None,
                          block_table[:singles], n_heads, n_kv, head_dim, window, scale,
-                         decode_splits(singles, n_kv, min(ctx.max_ctx, window or (1 << 30))), slopes=score_slopes,
+                         decode_splits(singles, groups, min(ctx.max_ctx, window or (1 << 30))), slopes=score_slopes,
                          split_weights=exact_weights, sinks=sinks)
     q_start, start_pos, table, n_req = ctx.q_start, ctx.start_pos, block_table, ctx.n_requests
     if 0 < singles < ctx.n_requests:

@@ -80,6 +80,13 @@ class GatedMLP:
     def forward(self, xn, ctx):
         # gate and up stay float32 until the activation has been applied; the down
         # projection's float32 result goes into the residual stream unrounded
+        n = xn.shape[0]
+        if (kernels.skinny_fits(n, self.hidden, self.dtype) and kernels.skinny_fits(n, self.inter, self.dtype)
+                and xn.is_contiguous()):
+            # a step of a few rows: both products stream their weights once, the activation in the first one's epilogue
+            act = kernels.skinny_gemm(self.w_gate_up[:self.inter], weight_up=self.w_gate_up[self.inter:], x=xn,
+                                      epilogue="swiglu", prefetch=self._target(0))
+            return kernels.skinny_gemm(self.w_down, x=act, epilogue="f32", prefetch=self._target(1))
         act = self._activation(xn)
         return kernels.linear(act, self.w_down, out_dtype=torch.float32)
 
