@@ -406,3 +406,77 @@ def test_table_experts_clamped_activation_and_shared_expert(dtype, E, top, d, f,
     got2 = part.forward(_t(h, dtype), types.SimpleNamespace(token_ids=_t(dev_ids, "int32"),
                                                             last_token=_t(last, "int32"))).cpu().numpy()
     assert np.array_equal(got, got2)
+
+
+# ---- configurations drawn at random -----------------------------------------------------------------
+
+def draw_config(seed):
+    """Sizes that are and are not multiples of what the kernels like, every branch of the design."""
+    rng = np.random.default_rng(7000 + seed)
+    width = int(rng.choice([24, 40, 50, 64, 72, 96, 128, 136]))
+    n_layers = int(rng.integers(2, 6))
+    streams = int(rng.choice([0, 1, 2, 3, 4, 6, 9]))
+    layers, owners = [], []
+    for i in range(n_layers):
+        src = None
+        if owners and rng.random() < 0.4:
+            src = int(rng.choice(owners))
+        R = layers[src]["mixer"]["kv_rank"] if src is not None else int(rng.choice([8, 10, 16, 24, 32, 48, 64, 80, 96, 112, 128,
+                                                                                    144, 160, 192, 256]))
+        window = None if rng.random() < 0.2 else int(rng.choice([1, 3, 16, 17, 40, 64, 100, 130]))
+        m = _mix(int(rng.choice([1, 2, 3, 4, 6, 8, 12, 20])), int(rng.choice([4, 6, 8, 16, 24, 32])),
+                 int(rng.choice([4, 5, 8, 16, 20, 40])), int(rng.choice([6, 8, 16, 24, 40])), R,
+                 float(rng.choice([0.2, 0.35, 0.5])), window=window, kv_from=src)
+        if src is None:
+            owners.append(i)
+        kind = rng.choice(["dense", "moe", "moe_shared", "none"])
+        if kind == "dense":
+            mlp = {"kind": "dense", "ff": int(rng.choice([16, 24, 50, 64]))}
+        elif kind == "none":
+            mlp = None
+        else:
+            E = int(rng.choice([2, 3, 4, 8]))
+            mlp = _moe(int(rng.choice([8, 12, 24, 33])), float(rng.choice([0.7, 1.0, 2.5])), E, int(rng.integers(1, E + 1)),
+                       shared=(int(rng.choice([8, 20, 32])), float(rng.choice([0.5, 1.25]))) if kind == "moe_shared" else None)
+        layers.append(_layer(m, mlp))
+    cfg = {"architecture": "Nutizen", "vocab": int(rng.choice([61, 97, 128, 300])), "width": width,
+           "embedding": {"scale": float(rng.choice([1.0, 2.0, 5.5]))}, "norm": {"eps": float(rng.choice([1e-5, 1e-6]))},
+           "layers": layers}
+    if streams:
+        cfg["streams"] = streams
+    return cfg
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("seed", range(12))
+def test_drawn_configuration(tmp_path, seed, dtype):
+    """A whole prompt, most of it and then its last tokens one by one, and three requests decoding side
+    by side, for a configuration drawn at random."""
+    from kllm_b200.engine.step import StepEntry
+    cfg = draw_config(seed)
+    w = P.random_weights(cfg, 900 + seed, qk_boost=2.0)
+    d = write_model_dir(str(tmp_path / "m"), cfg,
+                        {k: (np.asarray(v, dtype=np.float32) if v.dtype != np.int32 else v) for k, v in w.items()})
+    rng = np.random.default_rng(seed)
+    page = int(rng.choice([16, 32, 64]))
+    eng = engine_for(d, dtype, max_seq=256, block_size=page, num_blocks=1024 // page)
+    what = f"drawn {seed} {dtype}"
+    try:
+        ids = rng.integers(0, cfg["vocab"], size=int(rng.integers(140, 200))).tolist()
+        want = P.forward(w, cfg, ids)
+        check_rows(run_cut(eng, ids, [len(ids)]), want, dtype, what + " whole")
+        check_rows(run_cut(eng, ids, [len(ids) - 9, 1]), want, dtype, what + " prompt then decode")
+        check_rows(run_cut(eng, ids, [5, 2, 50, 1, 1, 33]), want, dtype, what + " portions")
+        seqs = [rng.integers(0, cfg["vocab"], size=n).tolist() for n in (9, 33, 150)]
+        wants = [P.forward(w, cfg, s) for s in seqs]
+        reqs = [eng.cache.open() for _ in seqs]
+        eng.runner.run([StepEntry(r, s[:-4], []) for r, s in zip(reqs, seqs)])
+        for back in range(4, 0, -1):
+            got = eng.runner.run([StepEntry(r, [s[-back]], [0]) for r, s in zip(reqs, seqs)]).float().cpu().numpy()
+            for j, (s, wj) in enumerate(zip(seqs, wants)):
+                check_rows(got[j:j + 1], wj[len(s) - back:len(s) - back + 1], dtype, what + f" batch of 3, request {j}")
+        for r in reqs:
+            eng.cache.close(r)
+        eng.cache.audit()
+    finally:
+        eng.close()
