@@ -952,8 +952,27 @@ def design_comparison(args):
                 kernels.moe_combine(kernels.moe_gemm(act, dn, offsets, perm, wt, top, gated=False, scale_out=True), top)
             us = timed(experts, inner=2) * 1e3
             used = min(E, n * top)
-            note(f"table experts ({top} of {E}) {name}", us, 3.0 * used * eff * width * esz,
+            note(f"table experts ({top} of {E}), grouped kernels, {name}", us, 3.0 * used * eff * width * esz,
                  6.0 * n * top * eff * width if dtype == "bfloat16" else 0, like=f"llama gate/up/down {name}")
+            if n * top >= 128 * E:
+                # the route a large step takes when the host knows its ids: sorted there, the library's products
+                # expert by expert (``RoutedExperts._forward_planned``)
+                from kllm_b200.parts.moe import RoutedExperts
+                from kllm_b200.parts.spec import BuildEnv, PartSpec
+                part = RoutedExperts(PartSpec("routed_experts", "", {
+                    "hidden": width, "experts": E, "top": top, "expert_ff": eff, "routing": "table", "table_tensor": "table",
+                    "vocab": 32000, "weight_on": "output", "activation": "clamped", "limit": 7.0, "alpha": 1.702,
+                    "expert_tensors": "e{e}.{m}"}), BuildEnv(tdt, torch.device(dev), width, 1 << 20))
+                gu0, dn0 = wsets[0]
+                tensors = {"table": tab}
+                for e in range(E):
+                    tensors[f"e{e}.gate"], tensors[f"e{e}.up"], tensors[f"e{e}.down"] = gu0[e, :eff], gu0[e, eff:], dn0[e]
+                part.bind(tensors)
+                import types as _types
+                c = _types.SimpleNamespace(token_ids=ids, last_token=None, host_token_ids=ids.cpu().numpy())
+                us = timed(lambda: part.forward(x, c), inner=2) * 1e3
+                note(f"table experts ({top} of {E}), sorted by the host, {name}", us, 3.0 * used * eff * width * esz,
+                     6.0 * n * top * eff * width if dtype == "bfloat16" else 0, like=f"llama gate/up/down {name}")
             dsets = rotate(lambda: ((torch.randn(2 * ff, width, device=dev) * 0.02).to(tdt),
                                     (torch.randn(width, ff, device=dev) * 0.02).to(tdt)), 3 * ff * width * esz)
             resid = torch.zeros(n, width, device=dev)

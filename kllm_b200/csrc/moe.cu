@@ -393,7 +393,7 @@ int launch_mma(void* c, const void* a, int64_t a_stride, const void* w, const in
 
 __global__ void __launch_bounds__(256)
 combine_kernel(float* __restrict__ y, const float* __restrict__ parts, int64_t total, int d, int top,
-               const float* __restrict__ shared, const float* __restrict__ gate, int64_t gate_stride) {
+               const float* __restrict__ shared, const float* __restrict__ gate, int64_t gate_stride, float scale) {
     griddep_wait();
     griddep_launch();
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -401,6 +401,7 @@ combine_kernel(float* __restrict__ y, const float* __restrict__ parts, int64_t t
         const int c = (int)(i - t * d);
         float s = 0.f;
         for (int j = 0; j < top; j++) s += parts[(t * top + j) * d + c];
+        s *= scale;
         if (shared) s += shared[i] * (gate ? 1.f / (1.f + expf(-gate[t * gate_stride])) : 1.f);
         y[i] = s;
     }
@@ -504,15 +505,15 @@ extern "C" int kllm_moe_table_route(int* idx, float* wt, const int* token_ids, c
     KLLM_LAUNCH_STATUS();
 }
 
-// y[t] = sum of parts[t * top + j] over j in order (+ shared[t] * sigmoid(gate[t * gate_stride]) when
+// y[t] = scale * (sum of parts[t * top + j] over j in order) (+ shared[t] * sigmoid(gate[t * gate_stride]) when
 // `shared` float32 [n][d] is given; gate NULL: the shared rows are added as they are).
 extern "C" int kllm_moe_combine(float* y, const float* parts, int n, int d, int top, const float* shared,
-                                const float* gate, int64_t gate_stride, void* stream) {
+                                const float* gate, int64_t gate_stride, float scale, void* stream) {
     if (n <= 0) return 0;
     const int64_t total = (int64_t)n * d;
     int64_t blocks = (total + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     kllm_launch((combine_kernel), dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, y, parts, total, d, top,
-                shared, gate, gate_stride);
+                shared, gate, gate_stride, scale);
     KLLM_LAUNCH_STATUS();
 }

@@ -246,7 +246,8 @@ class StepRunner:
             block_tables=tables, want_rows=part(7)[:R], n_want=R,
             host_n_new=n_new, host_start_pos=start, max_new=max(n_new),
             max_ctx=max(s + c for s, c in zip(start, n_new)), all_single=all(c == 1 for c in n_new),
-            last_token=self.last_token)
+            last_token=self.last_token,
+            host_token_ids=None if any(e.deferred for e in entries) else h[offs[0]:offs[1]].copy())
 
     # ---- run ---------------------------------------------------------------
     def run(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:

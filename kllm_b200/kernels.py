@@ -1208,13 +1208,14 @@ def moe_gemm(a: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, perm: torc
 
 
 def moe_combine(parts: torch.Tensor, top: int, shared: Optional[torch.Tensor] = None,
-                gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                gate: Optional[torch.Tensor] = None, scale: float = 1.0) -> torch.Tensor:
     """y[t] = sum of parts[t * top + j] over j in order; float32.  With ``shared`` (float32
     [n, d], the output of an expert that every token runs) also + shared[t] * sigmoid(gate[t]),
-    ``gate`` being a float32 column of one logit per token (None: the rows are added as they are)."""
+    ``gate`` being a float32 column of one logit per token (None: the rows are added as they are).
+    ``scale`` multiplies the sum over j (one weight that all of a token's choices share)."""
     _cuda(parts, shared, gate)
-    if top == 1 and shared is None:
-        return parts
+    if top == 1 and shared is None and scale == 1.0:
+        return parts            # nothing to add up: the rows themselves
     n, d = parts.shape[0] // top, parts.shape[1]
     if not parts.is_contiguous() or parts.dtype != torch.float32:
         raise KernelError("moe_combine: the experts' rows must be contiguous float32")
@@ -1225,7 +1226,7 @@ def moe_combine(parts: torch.Tensor, top: int, shared: Optional[torch.Tensor] = 
     y = torch.empty((n, d), dtype=torch.float32, device=parts.device)
     lib = load_library("moe")
     rc = lib.kllm_moe_combine(_p(y), _p(parts), n, d, int(top), _p(shared), _p(gate),
-                              ctypes.c_int64(gate.stride(0) if gate is not None else 0), _stream())
+                              ctypes.c_int64(gate.stride(0) if gate is not None else 0), ctypes.c_float(scale), _stream())
     _check(lib, "moe", rc)
     return y
 

@@ -42,6 +42,8 @@ class StepContext:
     all_single: bool = False   # every request brings exactly one token
     split_bound: int = 0       # context bound that fixes launch shapes (0: use max_ctx)
     last_token: Optional[torch.Tensor] = None   # int32 [request slots]: the sampler's latest choice per slot
+    host_token_ids: Optional[object] = None     # numpy int32 [n_tokens] when the host knows every id of the step
+                                                # (no id is still on the device): a part may plan its launches by them
 
 
 @dataclass

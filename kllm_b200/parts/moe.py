@@ -21,6 +21,11 @@ an id that is still on the device from the step before is resolved there).
 ``activation`` "clamped" with ``limit`` L and ``alpha`` a: the expert computes
 W_down (g sigmoid(a g) (u + 1)) with g = min(W_gate x, L), u = clamp(W_up x, -L, L) instead
 of silu(W_gate x) * (W_up x).
+``planned_rows`` (128): with a table, a step whose ids the host knows and that brings at least this
+many rows per expert on average is sorted by the host: every expert's rows become a block padded to
+the fullest expert's count and the experts' products two batched products of the library (the
+grouped kernels find their ranges on the device and reach a sixth of the library's speed over a
+prompt); not when one expert's share would make the padding more than double the work.
 ``shared``: a dict {``ff``, ``activation``, ``limit``, ``alpha``, ``tensors`` (gate, up, down and
 optionally gate_logit -> full names)}: one more expert that every token runs, added to the
 routed ones, multiplied by sigmoid(w . x) when ``gate_logit`` names a [1, d] tensor.  Its gate,
@@ -65,6 +70,9 @@ class RoutedExperts:
         if self.routing == "table" and self.table_vocab <= 0:
             raise ValueError("routed experts: a routing table needs the vocabulary's size ('vocab')")
         self.act = self._activation(p)
+        # a step with at least this many rows per expert on average, a table and ids that the host knows runs
+        # the library's products expert by expert (``_forward_planned``); below it the grouped kernels
+        self.planned_rows = int(p.get("planned_rows") or 128)
         sh = p.get("shared")
         self.shared = None
         if sh:
@@ -104,6 +112,8 @@ class RoutedExperts:
     def bind(self, tensors):
         self.router = tensors[self.router_name] if self.routing == "scores" else None
         self.table = tensors[self.table_name].contiguous() if self.routing == "table" else None
+        # for steps planned on the host; 16-bit, which numpy sorts by radix
+        self.table_host = self.table.cpu().numpy().astype("int16") if self.routing == "table" else None
         if self.shared:
             n = self.shared["names"]
             rows = [tensors[n["gate"]], tensors[n["up"]]] + ([tensors[n["gate_logit"]]] if n.get("gate_logit") else [])
@@ -125,7 +135,58 @@ class RoutedExperts:
         rows = kernels.linear(act, sh["w_down"], out_dtype=torch.float32, small_ok=True)
         return rows, (gu[:, 2 * f:] if gu.shape[1] > 2 * f else None)
 
+    def _plan(self, ctx, n):
+        """The host's sort of a step's (token, choice) pairs by expert, for a table and ids that the host knows:
+        (rows per expert padded to the fullest expert's count, for every padded row the token it reads, for
+        every pair its padded row), or None when one expert has so many rows that padding would more than
+        double the work."""
+        import numpy as np
+        top, E = self.top, self.experts
+        flat = self.table_host[ctx.host_token_ids].reshape(-1)
+        counts = np.bincount(flat, minlength=E)
+        width = int(counts.max())
+        if width * E > 2 * n * top:
+            return None
+        order = np.argsort(flat, kind="stable")
+        starts = np.concatenate([[0], np.cumsum(counts)[:-1]])
+        sorted_expert = flat[order].astype(np.int64)
+        padded = sorted_expert * width + (np.arange(n * top) - starts[sorted_expert])     # sorted row -> padded row
+        src = np.zeros(E * width, dtype=np.int32)              # rows that pad an expert read token 0; nobody reads them back
+        src[padded] = order // top
+        back = np.empty(n * top, dtype=np.int32)
+        back[order] = padded
+        return width, src, back
+
+    def _forward_planned(self, xn, plan):
+        """A large step sorted by the host: every expert's rows are a block of equal (padded) height, so the
+        experts' products are two batched products of the library over gathered rows."""
+        n, top, E, f = xn.shape[0], self.top, self.experts, self.ff
+        import numpy as np
+        width, src, back = plan
+        host = torch.from_numpy(np.concatenate([src, back]))
+        if xn.is_cuda:
+            host = host.pin_memory()
+        idx = host.to(xn.device, non_blocking=True)
+        xs = torch.empty((E * width, self.hidden), dtype=self.dtype, device=xn.device)
+        kernels.gather_rows(xs, xn, idx[:E * width])
+        gu = kernels.linear_batched(xs.view(E, width, self.hidden), self.w_gate_up).view(E * width, 2 * f)
+        act = torch.empty((E * width, f), dtype=self.dtype, device=xn.device)
+        if self.act["activation"] == "clamped":
+            kernels.clamped_glu(act, gu[:, :f], gu[:, f:], self.act["limit"], self.act["alpha"])
+        else:
+            kernels.silu_mul(act, gu[:, :f], gu[:, f:])
+        rows = kernels.linear_batched(act.view(E, width, f), self.w_down).view(E * width, self.hidden)
+        parts = torch.empty((n * top, self.hidden), dtype=torch.float32, device=xn.device)
+        kernels.gather_rows(parts, rows, idx[E * width:])
+        shared, logit = self._shared(xn) if self.shared is not None else (None, None)
+        return kernels.moe_combine(parts, top, shared=shared, gate=logit, scale=self.table_weight)
+
     def forward(self, xn, ctx):
+        if (self.routing == "table" and self.weight_on == "output" and getattr(ctx, "host_token_ids", None) is not None
+                and xn.shape[0] * self.top >= self.planned_rows * self.experts):
+            plan = self._plan(ctx, xn.shape[0])
+            if plan is not None:
+                return self._forward_planned(xn, plan)
         if self.routing == "table":
             idx, wt = kernels.moe_table_route(ctx.token_ids, self.table, self.experts, self.table_weight, ctx.last_token)
         else:

@@ -406,6 +406,14 @@ def test_table_experts_clamped_activation_and_shared_expert(dtype, E, top, d, f,
     got2 = part.forward(_t(h, dtype), types.SimpleNamespace(token_ids=_t(dev_ids, "int32"),
                                                             last_token=_t(last, "int32"))).cpu().numpy()
     assert np.array_equal(got, got2)
+    # a step whose ids the host knows and that is large enough is sorted by the host and runs the
+    # library's batched products over blocks of rows: the same numbers up to the order of the sums
+    part.planned_rows = 1
+    known = types.SimpleNamespace(token_ids=_t(ids, "int32"), last_token=None, host_token_ids=ids.astype(np.int32))
+    assert (E, top) not in ((8, 2), (3, 3)) or part._plan(known, n) is not None       # those do take that route
+    got3 = part.forward(_t(h, dtype), known).cpu().numpy()
+    assert np.abs(got3 - want).max() <= tol * np.abs(want).max()
+    assert np.abs(got3 - got).max() <= (1e-5 if dtype == "float32" else 2e-2) * np.abs(want).max()
 
 
 # ---- configurations drawn at random -----------------------------------------------------------------
