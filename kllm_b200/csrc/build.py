@@ -59,7 +59,7 @@ def build_dir() -> str:
     for d in cands:
         try:
             os.makedirs(d, exist_ok=True)
-            probe = os.path.join(d, f".w{os.getpid()}")
+            probe = os.path.join(d, f".w{os.getpid()}-{threading.get_ident()}")
             with open(probe, "w"):
                 pass
             os.unlink(probe)
@@ -227,12 +227,13 @@ VARIANTS = {"attention_tc": [{"KLLM_HD": hd} for hd in list(range(16, 129, 16)) 
             "attention_tcgen05_ptmem": [{"KLLM_HD": hd} for hd in (64, 128)]}
 
 
-def build_all(verbose: bool = True) -> List[str]:
-    out = []
-    for n in sources():
-        for defines in VARIANTS.get(n, [None]):
-            out.append(compile_library(n, verbose=verbose, defines=defines))
-    return out
+def build_all(verbose: bool = True, jobs: int = 0) -> List[str]:
+    """Compile every library and every variant, ``jobs`` compilations at a time (0: one per core, at most 8)."""
+    from concurrent.futures import ThreadPoolExecutor
+    todo = [(n, defines) for n in sources() for defines in VARIANTS.get(n, [None])]
+    jobs = jobs or max(1, min(8, os.cpu_count() or 1))
+    with ThreadPoolExecutor(max_workers=jobs) as pool:
+        return list(pool.map(lambda nd: compile_library(nd[0], verbose=verbose, defines=nd[1]), todo))
 
 
 if __name__ == "__main__":

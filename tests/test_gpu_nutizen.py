@@ -4,7 +4,7 @@ Small configurations of their own, random weights whose values are bfloat16 numb
 dtypes load the same model): each mechanism's kernel alone, whole prompts, prompts against
 token-by-token decoding, portions down to two tokens, unequal batches, slots and pages that
 are used again, keys far away, at page borders and just inside and outside a window that one
-score makes stand out, sinks that dominate, the first tokens, long decoding through CUDA
+score makes stand out, sinks that take a visible share, the first tokens, long decoding through CUDA
 graphs, and greedy generation through the scheduler.
 """
 import numpy as np
